@@ -1,0 +1,61 @@
+// Shared device helpers for the horizontally fused kernels (sm_100a only).
+//
+// A fused kernel splits one thread block into two contiguous thread ranges
+// ("roles").  The shape follows what aoli-al/HFuse emits: range guards
+// (lib/KernelFuser/KernelFusion.cpp:5-10), thread ids re-derived from the
+// range start (lib/KernelFuser/ThreadInfoRewriter.cpp:38-58) and every
+// block-wide barrier replaced by a named partial barrier `bar.sync id, count`
+// with one id per original kernel, counting from 1
+// (lib/KernelFuser/BarrierRewriter.cpp:12-28).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ < 1000)
+#error "hfuse_b200 kernels are written for sm_100a only"
+#endif
+
+namespace hfuse {
+
+// Barrier 0 belongs to __syncthreads(); roles use ids 1 and 2 so that one
+// role can never release or block the other.
+template <int ID, int COUNT>
+__device__ __forceinline__ void role_sync() {
+    static_assert(ID >= 1 && ID <= 15, "named barrier id out of range");
+    static_assert(COUNT % 32 == 0 && COUNT > 0, "a role is a whole number of warps");
+    asm volatile("bar.sync %0, %1;" ::"n"(ID), "n"(COUNT) : "memory");
+}
+
+// ---- streaming global accesses -------------------------------------------------
+// Inputs are read once and outputs written once, so loads bypass L1
+// allocation and stores are marked evict-first.
+__device__ __forceinline__ float4 ldg_stream4(const float* p) {
+    float4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void stg_stream4(float* p, float4 v) {
+    asm volatile("st.global.cs.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ void stg_stream1(float* p, float v) {
+    asm volatile("st.global.cs.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+__device__ __forceinline__ void stg_stream_2xi64(long long* p, long long a, long long b) {
+    asm volatile("st.global.cs.v2.s64 [%0], {%1,%2};" ::"l"(p), "l"(a), "l"(b) : "memory");
+}
+
+// ---- role context ----------------------------------------------------------------
+// What a role body sees instead of threadIdx / blockDim: its own thread id
+// inside the range and the range size T (a compile-time constant).  blockIdx
+// and gridDim are shared by both roles, exactly as in the reference's output
+// (ThreadInfoRewriter rewrites threadIdx and blockDim only).
+struct RoleCtx {
+    int tid;        // 0 .. T-1 inside the role's thread range
+    int block;      // blockIdx.x
+    int nblocks;    // gridDim.x
+    unsigned char* smem;   // this role's private slice of dynamic shared memory
+};
+
+}  // namespace hfuse

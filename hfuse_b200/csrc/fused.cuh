@@ -1,0 +1,40 @@
+// Kernel shells: one role over a whole block (the unfused baseline) and two
+// roles side by side in one block (the horizontally fused pair).
+//
+// The fused shell is the hand-written form of what the reference prints for
+// its `hfuse` presets: `__launch_bounds__(T1+T2, minBlocks)`
+// (lib/KernelFuser/KernelPrinter.cpp:44-65), parameter lists concatenated
+// (KernelPrinter.cpp:107-114), body 1 guarded by `tid < T1` and body 2 by
+// `T1 <= tid < T1+T2` (lib/KernelFuser/KernelFusion.cpp:5-10,
+// lib/KernelFuser/KernelFuseTool.cpp:56-62).  The split T1:T2 is a template
+// parameter so that the sweep of tools/llvm-smart-fuser/main.cpp:215-227
+// (128-thread steps) becomes a list of instantiations.
+#pragma once
+#include "common.cuh"
+
+namespace hfuse {
+
+template <class Role, int T, int MINB>
+__global__ void __launch_bounds__(T, MINB) solo_kernel(const __grid_constant__ typename Role::Args a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    RoleCtx ctx{(int)threadIdx.x, (int)blockIdx.x, (int)gridDim.x, smem};
+    Role::template run<T, 1>(a, ctx);
+}
+
+template <class RoleA, class RoleB, int TA, int TB, int MINB>
+__global__ void __launch_bounds__(TA + TB, MINB)
+fused_kernel(const __grid_constant__ typename RoleA::Args a, const __grid_constant__ typename RoleB::Args b,
+             int smem_off_b) {
+    static_assert(TA % 32 == 0 && TB % 32 == 0, "ranges are whole warps, so the guard never splits a warp");
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int tid = (int)threadIdx.x;
+    if (tid < TA) {
+        RoleCtx ctx{tid, (int)blockIdx.x, (int)gridDim.x, smem};
+        RoleA::template run<TA, 1>(a, ctx);
+    } else {
+        RoleCtx ctx{tid - TA, (int)blockIdx.x, (int)gridDim.x, smem + smem_off_b};
+        RoleB::template run<TB, 2>(b, ctx);
+    }
+}
+
+}  // namespace hfuse

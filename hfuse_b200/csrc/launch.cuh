@@ -1,0 +1,115 @@
+// Host-side launch plumbing shared by the DL and crypto entry points:
+// per-device facts, occupancy cache, the per-pair tuning table and the
+// variant dispatchers.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <tuple>
+
+#include "../../include/hfuse_b200.h"
+#include "fused.cuh"
+
+namespace hfuse {
+
+struct DeviceFacts {
+    int sms = 0;
+    int cc_major = 0;
+};
+
+inline int device_facts(DeviceFacts& out) {
+    static std::mutex mu;
+    static std::map<int, DeviceFacts> cache;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return HFUSE_ERR_NO_DEVICE;
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = cache.find(dev);
+    if (it == cache.end()) {
+        DeviceFacts f;
+        if (cudaDeviceGetAttribute(&f.sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&f.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
+            return HFUSE_ERR_NO_DEVICE;
+        if (f.cc_major != 10) return HFUSE_ERR_NO_DEVICE;   // sm_100a code only
+        it = cache.emplace(dev, f).first;
+    }
+    out = it->second;
+    return HFUSE_OK;
+}
+
+// resident blocks per SM of (kernel, block size, dynamic smem) on the current device
+inline int resident_blocks(const void* func, int block, size_t smem) {
+    static std::mutex mu;
+    static std::map<std::tuple<int, const void*, int, size_t>, int> cache;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto key = std::make_tuple(dev, func, block, smem);
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, func, block, smem) != cudaSuccess || n < 1) n = 1;
+    cache[key] = n;
+    return n;
+}
+
+// ---- tuning table ------------------------------------------------------------------
+struct Tune {
+    int variant = -1;         // -1: the pair's compiled default
+    int blocks_per_sm = 0;    // 0: as many as are resident
+};
+
+inline std::map<std::string, Tune>& tune_table() {
+    static std::map<std::string, Tune> t;
+    return t;
+}
+inline std::mutex& tune_mutex() {
+    static std::mutex m;
+    return m;
+}
+inline Tune tune_get(const char* name) {
+    std::lock_guard<std::mutex> lk(tune_mutex());
+    auto it = tune_table().find(name);
+    return it == tune_table().end() ? Tune{} : it->second;
+}
+
+inline int check_launch() { return cudaGetLastError() == cudaSuccess ? HFUSE_OK : HFUSE_ERR_LAUNCH; }
+
+// ---- one role over the whole block ----------------------------------------------------
+template <class Role, int T, int MINB>
+int launch_solo(typename Role::Args a, int blocks_per_sm, cudaStream_t s) {
+    DeviceFacts f;
+    if (int rc = device_facts(f)) return rc;
+    auto kern = solo_kernel<Role, T, MINB>;
+    // shared memory of every role on this path does not depend on the grid
+    if (int rc = Role::plan(a, T, f.sms * (blocks_per_sm > 0 ? blocks_per_sm : MINB))) return rc;
+    const size_t smem = (size_t)Role::smem_bytes(a, T);
+    const int bps = blocks_per_sm > 0 ? blocks_per_sm : resident_blocks((const void*)kern, T, smem);
+    const int grid = f.sms * bps;
+    if (int rc = Role::plan(a, T, grid)) return rc;
+    kern<<<grid, T, smem, s>>>(a);
+    return check_launch();
+}
+
+// ---- two roles side by side ------------------------------------------------------------
+template <class RA, class RB, int TA, int TB, int MINB>
+int launch_pair(typename RA::Args a, typename RB::Args b, int blocks_per_sm, cudaStream_t s) {
+    DeviceFacts f;
+    if (int rc = device_facts(f)) return rc;
+    auto kern = fused_kernel<RA, RB, TA, TB, MINB>;
+    if (int rc = RA::plan(a, TA, f.sms * MINB)) return rc;
+    if (int rc = RB::plan(b, TB, f.sms * MINB)) return rc;
+    const int smem_a = (RA::smem_bytes(a, TA) + 15) & ~15;
+    const size_t smem = (size_t)smem_a + (size_t)RB::smem_bytes(b, TB);
+    const int bps = blocks_per_sm > 0 ? blocks_per_sm : resident_blocks((const void*)kern, TA + TB, smem);
+    const int grid = f.sms * bps;
+    if (int rc = RA::plan(a, TA, grid)) return rc;
+    if (int rc = RB::plan(b, TB, grid)) return rc;
+    kern<<<grid, TA + TB, smem, s>>>(a, b, smem_a);
+    return check_launch();
+}
+
+}  // namespace hfuse

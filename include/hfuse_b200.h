@@ -1,0 +1,234 @@
+/*
+ * hfuse_b200 — C ABI of the horizontally fused kernel pairs for NVIDIA B200 (sm_100a).
+ *
+ * The reference (aoli-al/HFuse) has a source-level boundary: it prints fused
+ * `__global__` functions into `<K1>_<K2>_.inc` (tools/llvm-smart-fuser/main.cpp:247-257)
+ * whose parameter list is K1's parameters followed by K2's
+ * (lib/KernelFuser/KernelPrinter.cpp:107-114), and external host code launches them as
+ * `<<<grid, T1+T2, shmem, stream>>>(args of K1..., args of K2...)`
+ * (scripts/configs/hist_norm.json:5).  Each entry point below replaces one such launch
+ * site: same argument order (K1's then K2's, then the stream), buffers owned by the
+ * caller, results written in place, nothing allocated, nothing synchronised.
+ *
+ * Conventions
+ *   - every pointer is a device pointer on the current CUDA device unless its comment
+ *     says "host"; float buffers are contiguous NCHW fp32, 16-byte aligned;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the default stream);
+ *   - return value: HFUSE_OK or a negative HFUSE_ERR_* code; nothing is thrown;
+ *   - calls are asynchronous with respect to the host;
+ *   - thread-safe per (device, stream); the library holds no mutable state except the
+ *     tuning table changed by hfuse_tune_set().
+ */
+#ifndef HFUSE_B200_H
+#define HFUSE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define HFUSE_API __attribute__((visibility("default")))
+#else
+#define HFUSE_API
+#endif
+
+typedef void* hfuse_stream_t;
+
+enum {
+    HFUSE_OK = 0,
+    HFUSE_ERR_BAD_ARG = -1,     /* null pointer, non-positive extent, inconsistent shape */
+    HFUSE_ERR_ALIGNMENT = -2,   /* a buffer is not 16-byte aligned */
+    HFUSE_ERR_TOO_LARGE = -3,   /* an extent exceeds what the kernels index */
+    HFUSE_ERR_WORKSPACE = -4,   /* scratch buffer missing or too small */
+    HFUSE_ERR_LAUNCH = -5,      /* cudaGetLastError() after the launch was not cudaSuccess */
+    HFUSE_ERR_NO_DEVICE = -6,   /* no usable sm_100 device */
+    HFUSE_ERR_UNKNOWN_PAIR = -7
+};
+
+HFUSE_API const char* hfuse_error_string(int code);
+HFUSE_API int hfuse_version(void);
+
+/* ---------------------------------------------------------------------------------------
+ * Parameter lists of the nine kernels, in the reference kernels' own order, as macros
+ * so that a pair's prototype is literally "K1's parameters, K2's parameters".
+ * P is a prefix that keeps the names of the two halves apart.
+ * ------------------------------------------------------------------------------------- */
+
+/* at::native::im2col_kernel<float>(n, im, H, W, kh, kw, ph, pw, sh, sw, dh, dw, Hc, Wc, col)
+ * — configs/ml_kernels.yaml:28-36, scripts/data/ml-event.csv:17.  The reference launches it
+ * once per batch item; here N and C are explicit and one launch covers the batch.
+ * im [N,C,H,W] -> col [N, C*kh*kw, Hc*Wc], zero outside the image. */
+#define HFUSE_IM2COL_PARAMS(P)                                                              \
+    const float *P##im, int P##N, int P##C, int P##H, int P##W, int P##kh, int P##kw,       \
+        int P##ph, int P##pw, int P##sh, int P##sw, int P##dh, int P##dw, float *P##col
+
+/* at::native::MaxPoolForward<float,float>(nthreads, bottom, num, C, H, W, pH, pW, kh, kw, sh, sw,
+ * ph, pw, dh, dw, top, top_mask) — configs/ml_kernels.yaml:37-45, scripts/data/ml-event.csv:5.
+ * in [N,C,H,W] -> out [N,C,pH,pW] and idx (int64, h*W+w inside the plane). */
+#define HFUSE_MAXPOOL_PARAMS(P)                                                             \
+    const float *P##in, int P##N, int P##C, int P##H, int P##W, int P##pH, int P##pW,       \
+        int P##kh, int P##kw, int P##sh, int P##sw, int P##ph, int P##pw, int P##dh,        \
+        int P##dw, float *P##out, int64_t *P##idx
+
+/* at::native::batch_norm_collect_statistics_kernel<InvStd,float,float,float,int>(input[N][C][HW],
+ * eps, momentum, running_mean, running_var, save_mean, save_invstd)
+ * — configs/ml_kernels.yaml:19-27, scripts/data/ml-event.csv:14.  Running statistics are
+ * not touched (the reference pair passes them but the statistics kernel does not update
+ * them).  `moments` is optional (may be NULL): [C][3] doubles (n, n*mean, M2 + n*mean^2),
+ * the form that is summed across GPUs.  `workspace` is scratch of at least
+ * hfuse_bnstats_workspace_bytes() bytes, zero-filled once by the caller before its first
+ * use; each call leaves it ready for the next.  Two calls that overlap on the GPU must not
+ * share a workspace. */
+#define HFUSE_BNSTATS_PARAMS(P)                                                             \
+    const float *P##x, int P##N, int P##C, int P##HW, float P##eps, float *P##mean,         \
+        float *P##invstd, double *P##moments, void *P##workspace, size_t P##workspace_bytes
+
+/* at::native::upsample_bilinear2d_out_frame<float,float>(n, rheight, rwidth, align_corners,
+ * idata, odata) — configs/ml_kernels.yaml:1-9, scripts/data/ml-event.csv:32.  The scale
+ * factors are derived from the shapes the way the operator's host side does.
+ * in [N,C,H,W] -> out [N,C,outH,outW]. */
+#define HFUSE_UPSAMPLE_PARAMS(P)                                                            \
+    const float *P##in, int P##N, int P##C, int P##H, int P##W, int P##outH, int P##outW,   \
+        int P##align_corners, float *P##out
+
+/* at::native::kernelHistogram1D<float,float,long,1,2,-1,SHARED,Op>(a, p, b, nbins, minvalue,
+ * maxvalue, totalElements, getOp) — configs/ml_kernels.yaml:10-18, scripts/data/ml-event.csv:33.
+ * counts[nbins] (uint32) is cleared on the stream by the entry point, then accumulated. */
+#define HFUSE_HISTC_PARAMS(P)                                                               \
+    const float *P##x, int64_t P##n, int P##nbins, float P##lo, float P##hi, uint32_t *P##counts
+
+/* ---------------------------------------------------------------------------------------
+ * Standalone kernels: the unfused baseline a fused pair is compared with.
+ * ------------------------------------------------------------------------------------- */
+HFUSE_API int hfuse_im2col_f32(HFUSE_IM2COL_PARAMS(), hfuse_stream_t stream);
+HFUSE_API int hfuse_maxpool2d_f32(HFUSE_MAXPOOL_PARAMS(), hfuse_stream_t stream);
+HFUSE_API int hfuse_bnstats_f32(HFUSE_BNSTATS_PARAMS(), hfuse_stream_t stream);
+HFUSE_API int hfuse_upsample_bilinear2d_f32(HFUSE_UPSAMPLE_PARAMS(), hfuse_stream_t stream);
+HFUSE_API int hfuse_histc_f32(HFUSE_HISTC_PARAMS(), hfuse_stream_t stream);
+
+HFUSE_API size_t hfuse_bnstats_workspace_bytes(int N, int C, int HW);
+/* mean/invstd from moments already summed over GPUs (no counterpart in the reference,
+ * which is single-GPU): mean = s1/n, var = s2/n - mean^2, invstd = 1/sqrt(var + eps). */
+HFUSE_API int hfuse_bnstats_finalize_f64(const double* moments, int C, float eps, float* mean,
+                                         float* invstd, hfuse_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Fused pairs.  One kernel launch; the block is split into K1's and K2's thread ranges,
+ * each synchronising only on its own named barrier.  Order of the halves follows the
+ * reference's pair lists (configs/ml_fusion.yaml, line numbers beside each).
+ * ------------------------------------------------------------------------------------- */
+HFUSE_API int hfuse_im2col_maxpool_f32(HFUSE_IM2COL_PARAMS(a_), HFUSE_MAXPOOL_PARAMS(b_),
+                                       hfuse_stream_t stream);                        /* ml_fusion.yaml:1-4   */
+HFUSE_API int hfuse_im2col_bnstats_f32(HFUSE_IM2COL_PARAMS(a_), HFUSE_BNSTATS_PARAMS(b_),
+                                       hfuse_stream_t stream);                        /* ml_fusion.yaml:5-8   */
+HFUSE_API int hfuse_im2col_histc_f32(HFUSE_IM2COL_PARAMS(a_), HFUSE_HISTC_PARAMS(b_),
+                                     hfuse_stream_t stream);                          /* ml_fusion.yaml:9-12  */
+HFUSE_API int hfuse_im2col_upsample_f32(HFUSE_IM2COL_PARAMS(a_), HFUSE_UPSAMPLE_PARAMS(b_),
+                                        hfuse_stream_t stream);                       /* ml_fusion.yaml:13-16 */
+HFUSE_API int hfuse_maxpool_bnstats_f32(HFUSE_MAXPOOL_PARAMS(a_), HFUSE_BNSTATS_PARAMS(b_),
+                                        hfuse_stream_t stream);                       /* ml_fusion.yaml:17-20 */
+HFUSE_API int hfuse_maxpool_upsample_f32(HFUSE_MAXPOOL_PARAMS(a_), HFUSE_UPSAMPLE_PARAMS(b_),
+                                         hfuse_stream_t stream);                      /* ml_fusion.yaml:21-24 */
+HFUSE_API int hfuse_histc_maxpool_f32(HFUSE_HISTC_PARAMS(a_), HFUSE_MAXPOOL_PARAMS(b_),
+                                      hfuse_stream_t stream);                         /* ml_fusion.yaml:25-28 */
+HFUSE_API int hfuse_histc_upsample_f32(HFUSE_HISTC_PARAMS(a_), HFUSE_UPSAMPLE_PARAMS(b_),
+                                       hfuse_stream_t stream);                        /* ml_fusion.yaml:29-32 */
+HFUSE_API int hfuse_upsample_bnstats_f32(HFUSE_UPSAMPLE_PARAMS(a_), HFUSE_BNSTATS_PARAMS(b_),
+                                         hfuse_stream_t stream);                      /* ml_fusion.yaml:33-36 */
+HFUSE_API int hfuse_histc_bnstats_f32(HFUSE_HISTC_PARAMS(a_), HFUSE_BNSTATS_PARAMS(b_),
+                                      hfuse_stream_t stream);                         /* ml_fusion.yaml:37-40 */
+
+/* ---------------------------------------------------------------------------------------
+ * Crypto nonce searches.
+ *
+ * Reference kernels (configs/crypto_kernels.yaml:1-32, signatures in
+ * scripts/data/ethminer_event.csv:2-27):
+ *   ethash_search(volatile Search_results* g_output, uint64_t start_nonce)
+ *   blake2b_gpu_hash(uint32 threads, uint32 startNonce, uint32* resNonce, uint2 target2)
+ *       — the kernel the reference labels "Blake256" (scripts/analyze_nvprof.py:78)
+ *   sha256d_gpu_hash_shared(uint32 threads, uint32 startNonce, uint32* resNonces)
+ *   sia_blake2b_gpu_hash(uint32 threads, uint32 startNonce, uint32* resNonce, uint2 target2)
+ * Those kernels take header, target and DAG from __constant__ symbols; here they are
+ * arguments, so concurrent calls on different streams do not interfere.
+ *
+ * A digest is a hit iff its 32 bytes read as a big-endian 256-bit integer are below
+ * `target` (32 bytes, big-endian, host memory).  Headers are host memory.
+ *   BLAKE-256 (14 rounds) / SHA-256d : 80-byte header, 32-bit little-endian nonce at bytes
+ *       76..79; nonce = (uint32)(start + i), i < count <= 2^32.
+ *   Sia BLAKE2b-256 : 80-byte header, 64-bit little-endian nonce at bytes 32..39.
+ *   ethash : Keccak-512(header_hash[32] || nonce as 8 little-endian bytes), 64 DAG
+ *       accesses of 128 bytes, mix digest and Keccak-256 result per the public
+ *       specification; `dag` holds dag_items x 128 bytes on the device.
+ * ------------------------------------------------------------------------------------- */
+#define HFUSE_MAX_HITS 256
+
+/* The result record (replaces the reference's `Search_results`, whose layout is in the
+ * absent ethminer sources).  Device memory; `count` must be zero before a search
+ * (hfuse_hits_reset) and counts every hit found even beyond HFUSE_MAX_HITS; slots are
+ * filled in arrival order, so sort by nonce before comparing. */
+typedef struct hfuse_hits {
+    uint32_t count;
+    uint32_t reserved;
+    uint64_t nonce[HFUSE_MAX_HITS];
+    uint32_t mix[HFUSE_MAX_HITS][8];   /* ethash mix digest, little-endian words; zero otherwise */
+} hfuse_hits;
+
+HFUSE_API int hfuse_hits_reset(hfuse_hits* hits, hfuse_stream_t stream);
+
+#define HFUSE_BLAKE256_PARAMS(P)                                                            \
+    const uint8_t *P##header80, uint64_t P##start, uint64_t P##count, const uint8_t *P##target32, \
+        hfuse_hits *P##hits
+#define HFUSE_SHA256D_PARAMS(P) HFUSE_BLAKE256_PARAMS(P)
+#define HFUSE_SIA_PARAMS(P) HFUSE_BLAKE256_PARAMS(P)
+#define HFUSE_ETHASH_PARAMS(P)                                                              \
+    const void *P##dag, uint32_t P##dag_items, const uint8_t *P##header_hash32, uint64_t P##start, \
+        uint64_t P##count, const uint8_t *P##target32, hfuse_hits *P##hits
+
+HFUSE_API int hfuse_blake256_search(HFUSE_BLAKE256_PARAMS(), hfuse_stream_t stream);
+HFUSE_API int hfuse_sha256d_search(HFUSE_SHA256D_PARAMS(), hfuse_stream_t stream);
+HFUSE_API int hfuse_sia_blake2b_search(HFUSE_SIA_PARAMS(), hfuse_stream_t stream);
+HFUSE_API int hfuse_ethash_search(HFUSE_ETHASH_PARAMS(), hfuse_stream_t stream);
+
+/* pair order follows configs/crypto_fusion.yaml (line numbers beside each) */
+HFUSE_API int hfuse_ethash_blake256_search(HFUSE_ETHASH_PARAMS(a_), HFUSE_BLAKE256_PARAMS(b_),
+                                           hfuse_stream_t stream);                    /* crypto_fusion.yaml:1-4   */
+HFUSE_API int hfuse_sha256d_ethash_search(HFUSE_SHA256D_PARAMS(a_), HFUSE_ETHASH_PARAMS(b_),
+                                          hfuse_stream_t stream);                     /* crypto_fusion.yaml:5-8   */
+HFUSE_API int hfuse_sia_ethash_search(HFUSE_SIA_PARAMS(a_), HFUSE_ETHASH_PARAMS(b_),
+                                      hfuse_stream_t stream);                         /* crypto_fusion.yaml:9-12  */
+HFUSE_API int hfuse_blake256_sha256d_search(HFUSE_BLAKE256_PARAMS(a_), HFUSE_SHA256D_PARAMS(b_),
+                                            hfuse_stream_t stream);                   /* crypto_fusion.yaml:13-16 */
+HFUSE_API int hfuse_blake256_sia_search(HFUSE_BLAKE256_PARAMS(a_), HFUSE_SIA_PARAMS(b_),
+                                        hfuse_stream_t stream);                       /* crypto_fusion.yaml:17-20 */
+HFUSE_API int hfuse_sha256d_sia_search(HFUSE_SHA256D_PARAMS(a_), HFUSE_SIA_PARAMS(b_),
+                                       hfuse_stream_t stream);                        /* crypto_fusion.yaml:21-24 */
+
+/* Single-hash device evaluation for tests: digest (and ethash mix) of `count` consecutive
+ * nonces, written to out32[count][32] (and mix32[count][32], may be NULL unless kind 3).
+ * kind: 0 BLAKE-256, 1 SHA-256d, 2 Sia BLAKE2b, 3 ethash (header = header_hash32). */
+HFUSE_API int hfuse_hash_batch(int kind, const uint8_t* header, const void* dag, uint32_t dag_items,
+                               uint64_t start, uint32_t count, uint8_t* out32, uint8_t* mix32,
+                               hfuse_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Tuning (the reference sweeps the split in 128-thread steps and a launch-bound register
+ * cap per pair, tools/llvm-smart-fuser/main.cpp:182-236; here each pair has a compiled
+ * list of (T1, T2, blocks/SM) variants).  `pair` is the entry point's name without the
+ * "hfuse_" prefix and type suffix, e.g. "im2col_maxpool".  variant < 0 restores the
+ * default.  hfuse_tune_describe writes "T1:T2:minBlocks" of a variant into buf and
+ * returns the number of variants, or a negative error.
+ * ------------------------------------------------------------------------------------- */
+HFUSE_API int hfuse_tune_set(const char* pair, int variant, int blocks_per_sm);
+HFUSE_API int hfuse_tune_describe(const char* pair, int variant, char* buf, size_t buflen);
+
+/* Host utility: xoshiro256** byte stream (state = four splitmix64 outputs of `seed`,
+ * little-endian u64 words) — the generator the synthetic DAG and headers are drawn from. */
+HFUSE_API void hfuse_xoshiro256ss_fill(uint64_t seed, void* host_dst, size_t nbytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HFUSE_B200_H */
