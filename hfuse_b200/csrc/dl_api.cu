@@ -1,192 +1,8 @@
-// C-ABI entry points of the deep-learning kernels and their fused pairs.
-// Argument checking, role planning and variant dispatch live here; the device
-// code is in dl_roles.cuh and fused.cuh.
-#include "dl_roles.cuh"
-#include "launch.cuh"
-
-using namespace hfuse;
-
-// ---- argument-name lists matching the HFUSE_*_PARAMS macros of the public header ----------
-#define IM2COL_NAMES(P) P##im, P##N, P##C, P##H, P##W, P##kh, P##kw, P##ph, P##pw, P##sh, P##sw, P##dh, P##dw, P##col
-#define MAXPOOL_NAMES(P)                                                                                  \
-    P##in, P##N, P##C, P##H, P##W, P##pH, P##pW, P##kh, P##kw, P##sh, P##sw, P##ph, P##pw, P##dh, P##dw, \
-        P##out, P##idx
-#define BNSTATS_NAMES(P) P##x, P##N, P##C, P##HW, P##eps, P##mean, P##invstd, P##moments, P##workspace, P##workspace_bytes
-#define UPSAMPLE_NAMES(P) P##in, P##N, P##C, P##H, P##W, P##outH, P##outW, P##align_corners, P##out
-#define HISTC_NAMES(P) P##x, P##n, P##nbins, P##lo, P##hi, P##counts
+// C-ABI entry points of the standalone deep-learning kernels and the variant
+// descriptions.  The fused pairs live in dl_pair_*.cu.
+#include "dl_host.cuh"
 
 namespace {
-
-constexpr long long kMaxItems = (1LL << 31) - 1;
-
-inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-
-// ------------------------------------------------------------------ argument checking
-int prep_im2col(HFUSE_IM2COL_PARAMS(), Im2colArgs& a) {
-    if (!im || !col) return HFUSE_ERR_BAD_ARG;
-    if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || kh <= 0 || kw <= 0 || ph < 0 || pw < 0 || sh <= 0 || sw <= 0 ||
-        dh <= 0 || dw <= 0)
-        return HFUSE_ERR_BAD_ARG;
-    const long long eh = (long long)H + 2LL * ph - ((long long)dh * (kh - 1) + 1);
-    const long long ew = (long long)W + 2LL * pw - ((long long)dw * (kw - 1) + 1);
-    if (eh < 0 || ew < 0) return HFUSE_ERR_BAD_ARG;           // kernel larger than the padded image
-    const long long Hc = eh / sh + 1, Wc = ew / sw + 1;
-    if ((long long)H * W > kMaxItems || Hc * Wc > kMaxItems) return HFUSE_ERR_TOO_LARGE;
-    if (!aligned16(im) || !aligned16(col)) return HFUSE_ERR_ALIGNMENT;
-    a.im = im; a.col = col;
-    a.N = N; a.C = C; a.H = H; a.W = W;
-    a.kh = kh; a.kw = kw; a.ph = ph; a.pw = pw; a.sh = sh; a.sw = sw; a.dh = dh; a.dw = dw;
-    a.Hc = (int)Hc; a.Wc = (int)Wc;
-    const long long items = (long long)N * C * Hc * (Wc / 4);
-    a.mode = (kh == 3 && kw == 3 && sh == 1 && sw == 1 && dh == 1 && dw == 1 && (Wc % 4) == 0 && items > 0 &&
-              items <= kMaxItems)
-                 ? 1 : 0;
-    return HFUSE_OK;
-}
-
-int prep_maxpool(HFUSE_MAXPOOL_PARAMS(), MaxPoolArgs& a) {
-    if (!in || !out || !idx) return HFUSE_ERR_BAD_ARG;
-    if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || pH <= 0 || pW <= 0 || kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0 ||
-        ph < 0 || pw < 0 || dh <= 0 || dw <= 0)
-        return HFUSE_ERR_BAD_ARG;
-    if (ph > kh / 2 || pw > kw / 2) return HFUSE_ERR_BAD_ARG;                 // same rule as the operator
-    // every window must start inside the image (rules out pooled sizes the shape cannot give)
-    if ((long long)(pH - 1) * sh - ph >= H || (long long)(pW - 1) * sw - pw >= W) return HFUSE_ERR_BAD_ARG;
-    if ((long long)H * W > kMaxItems) return HFUSE_ERR_TOO_LARGE;
-    if (!aligned16(in) || !aligned16(out) || !aligned16(idx)) return HFUSE_ERR_ALIGNMENT;
-    a.in = in; a.out = out; a.idx = reinterpret_cast<long long*>(idx);
-    a.N = N; a.C = C; a.H = H; a.W = W; a.pH = pH; a.pW = pW;
-    a.kh = kh; a.kw = kw; a.sh = sh; a.sw = sw; a.ph = ph; a.pw = pw; a.dh = dh; a.dw = dw;
-    const long long items = (long long)N * C * pH * (pW / 4);
-    a.mode = (kh == 2 && kw == 2 && sh == 2 && sw == 2 && ph == 0 && pw == 0 && dh == 1 && dw == 1 &&
-              (pW % 4) == 0 && (W % 4) == 0 && 2LL * pH <= H && 2LL * pW <= W && items <= kMaxItems)
-                 ? 1 : 0;
-    return HFUSE_OK;
-}
-
-int prep_bnstats(HFUSE_BNSTATS_PARAMS(), BnStatsArgs& a) {
-    if (!x || !mean || !invstd) return HFUSE_ERR_BAD_ARG;
-    if (N <= 0 || C <= 0 || HW <= 0 || !(eps >= 0.f)) return HFUSE_ERR_BAD_ARG;
-    if ((long long)N * HW > kMaxItems) return HFUSE_ERR_TOO_LARGE;
-    if (!aligned16(x)) return HFUSE_ERR_ALIGNMENT;
-    if (workspace && !aligned16(workspace)) return HFUSE_ERR_ALIGNMENT;
-    a.x = x; a.N = N; a.C = C; a.HW = HW; a.eps = eps;
-    a.total = (float)((double)N * (double)HW);
-    a.mean = mean; a.invstd = invstd; a.moments = moments;
-    a.partial = nullptr; a.tickets = nullptr;
-    a.S = 1; a.ips = N;
-    a.vec = (HW % 4) == 0;
-    a.ws = workspace; a.ws_bytes = workspace_bytes;
-    return HFUSE_OK;
-}
-
-float scale_of(int in_size, int out_size, int align_corners) {
-    if (align_corners) return out_size > 1 ? (float)(in_size - 1) / (float)(out_size - 1) : 0.f;
-    return (float)in_size / (float)out_size;
-}
-
-int prep_upsample(HFUSE_UPSAMPLE_PARAMS(), UpsampleArgs& a) {
-    if (!in || !out) return HFUSE_ERR_BAD_ARG;
-    if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || outH <= 0 || outW <= 0) return HFUSE_ERR_BAD_ARG;
-    if ((long long)H * W > kMaxItems || (long long)outH * outW > kMaxItems) return HFUSE_ERR_TOO_LARGE;
-    if (!aligned16(in) || !aligned16(out)) return HFUSE_ERR_ALIGNMENT;
-    a.in = in; a.out = out; a.N = N; a.C = C; a.H = H; a.W = W; a.outH = outH; a.outW = outW;
-    a.rheight = scale_of(H, outH, align_corners);
-    a.rwidth = scale_of(W, outW, align_corners);
-    a.align_corners = align_corners ? 1 : 0;
-    const long long items = (long long)N * C * outH * (outW / 4);
-    a.mode = ((outW % 4) == 0 && items <= kMaxItems) ? 1 : 0;
-    return HFUSE_OK;
-}
-
-int prep_histc(HFUSE_HISTC_PARAMS(), HistcArgs& a) {
-    if (!counts || n < 0 || (n > 0 && !x)) return HFUSE_ERR_BAD_ARG;
-    if (nbins <= 0 || !(lo < hi)) return HFUSE_ERR_BAD_ARG;    // also rejects NaN bounds
-    if (nbins > (1 << 24)) return HFUSE_ERR_TOO_LARGE;         // bins must stay exact in fp32
-    if (x && !aligned16(x)) return HFUSE_ERR_ALIGNMENT;
-    a.x = x; a.n = n; a.nbins = nbins; a.lo = lo; a.hi = hi; a.counts = counts;
-    a.range = hi - lo;
-    int e = 0;
-    const float mant = frexpf(a.range, &e);
-    a.range_pow2 = (mant == 0.5f) && (e > -100) && (e < 100);
-    a.inv_range = a.range_pow2 ? 1.f / a.range : 0.f;
-    a.copies = 0;
-    return HFUSE_OK;
-}
-
-int clear_counts(const HistcArgs& a, cudaStream_t s) {
-    return cudaMemsetAsync(a.counts, 0, (size_t)a.nbins * sizeof(unsigned), s) == cudaSuccess ? HFUSE_OK
-                                                                                               : HFUSE_ERR_LAUNCH;
-}
-int pre_launch(const HistcArgs& a, cudaStream_t s) { return clear_counts(a, s); }
-template <class A> int pre_launch(const A&, cudaStream_t) { return HFUSE_OK; }
-
-// ------------------------------------------------------------------ variants
-// (index, T1, T2, minBlocks/SM).  Splits move in 128-thread steps like the reference's sweep
-// (tools/llvm-smart-fuser/main.cpp:215-227); minBlocks is the register cap of its `_lb`
-// presets (lib/KernelFuser/KernelPrinter.cpp:44-65) expressed as blocks per SM.
-#define DL_PAIR_VARIANTS(X)                                                                         \
-    X(0, 256, 256, 2) X(1, 384, 128, 2) X(2, 128, 384, 2) X(3, 256, 256, 3) X(4, 512, 512, 1)       \
-    X(5, 768, 256, 1) X(6, 256, 768, 1) X(7, 640, 384, 1) X(8, 384, 640, 1) X(9, 512, 256, 1)       \
-    X(10, 256, 512, 1) X(11, 128, 128, 4) X(12, 128, 128, 6) X(13, 896, 128, 1) X(14, 128, 896, 1)  \
-    X(15, 512, 256, 2) X(16, 256, 512, 2)
-constexpr int kDlPairVariants = 17;
-
-#define DL_SOLO_VARIANTS(X) X(0, 256, 4) X(1, 256, 8) X(2, 512, 2) X(3, 128, 8) X(4, 512, 4) X(5, 1024, 1) X(6, 128, 16)
-constexpr int kDlSoloVariants = 7;
-
-template <class RA, class RB>
-int dispatch_pair(const char* name, int default_variant, typename RA::Args a, typename RB::Args b, cudaStream_t s) {
-    const Tune t = tune_get(name);
-    const int v = t.variant >= 0 ? t.variant : default_variant;
-    if (int rc = pre_launch(a, s)) return rc;
-    if (int rc = pre_launch(b, s)) return rc;
-    switch (v) {
-#define X(I, TA, TB, MB) \
-    case I: return launch_pair<RA, RB, TA, TB, MB>(a, b, t.blocks_per_sm, s);
-        DL_PAIR_VARIANTS(X)
-#undef X
-    }
-    return HFUSE_ERR_BAD_ARG;
-}
-
-template <class R>
-int dispatch_solo(const char* name, int default_variant, typename R::Args a, cudaStream_t s) {
-    const Tune t = tune_get(name);
-    const int v = t.variant >= 0 ? t.variant : default_variant;
-    if (int rc = pre_launch(a, s)) return rc;
-    switch (v) {
-#define X(I, T, MB) \
-    case I: return launch_solo<R, T, MB>(a, t.blocks_per_sm, s);
-        DL_SOLO_VARIANTS(X)
-#undef X
-    }
-    return HFUSE_ERR_BAD_ARG;
-}
-
-int describe_dl_pair(int v, char* buf, size_t n) {
-    switch (v) {
-#define X(I, TA, TB, MB) \
-    case I: snprintf(buf, n, "%d:%d:%d", TA, TB, MB); return kDlPairVariants;
-        DL_PAIR_VARIANTS(X)
-#undef X
-    }
-    return HFUSE_ERR_BAD_ARG;
-}
-int describe_dl_solo(int v, char* buf, size_t n) {
-    switch (v) {
-#define X(I, T, MB) \
-    case I: snprintf(buf, n, "%d:0:%d", T, MB); return kDlSoloVariants;
-        DL_SOLO_VARIANTS(X)
-#undef X
-    }
-    return HFUSE_ERR_BAD_ARG;
-}
-
-// default variant per kernel / pair (index into the lists above), chosen by the sweep
-// in bench.py --tune on a B200
-#include "dl_tuned.inc"
-
 __global__ void bn_finalize_kernel(const double* mom, int C, float eps, float* mean, float* invstd) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= C) return;
@@ -200,7 +16,6 @@ __global__ void bn_finalize_kernel(const double* mom, int C, float eps, float* m
 }  // namespace
 
 // ------------------------------------------------------------------ exported symbols
-#define S_(x) static_cast<cudaStream_t>(x)
 
 extern "C" {
 
@@ -241,34 +56,6 @@ int hfuse_bnstats_finalize_f64(const double* moments, int C, float eps, float* m
     bn_finalize_kernel<<<(C + 127) / 128, 128, 0, S_(stream)>>>(moments, C, eps, mean, invstd);
     return check_launch();
 }
-
-#define DEFINE_PAIR(NAME, RA, PA, NA, prepA, ArgsA, RB, PB, NB, prepB, ArgsB)                          \
-    int hfuse_##NAME##_f32(PA(a_), PB(b_), hfuse_stream_t stream) {                                   \
-        ArgsA a;                                                                                       \
-        ArgsB b;                                                                                       \
-        if (int rc = prepA(NA(a_), a)) return rc;                                                      \
-        if (int rc = prepB(NB(b_), b)) return rc;                                                      \
-        return dispatch_pair<RA, RB>(#NAME, kDefaultPair_##NAME, a, b, S_(stream));                    \
-    }
-
-#define IM2COL_ Im2colRole, HFUSE_IM2COL_PARAMS, IM2COL_NAMES, prep_im2col, Im2colArgs
-#define MAXPOOL_ MaxPoolRole, HFUSE_MAXPOOL_PARAMS, MAXPOOL_NAMES, prep_maxpool, MaxPoolArgs
-#define BNSTATS_ BnStatsRole, HFUSE_BNSTATS_PARAMS, BNSTATS_NAMES, prep_bnstats, BnStatsArgs
-#define UPSAMPLE_ UpsampleRole, HFUSE_UPSAMPLE_PARAMS, UPSAMPLE_NAMES, prep_upsample, UpsampleArgs
-#define HISTC_ HistcRole, HFUSE_HISTC_PARAMS, HISTC_NAMES, prep_histc, HistcArgs
-#define DEFINE_PAIR_(NAME, A, B) DEFINE_PAIR_X(NAME, A, B)
-#define DEFINE_PAIR_X(NAME, ...) DEFINE_PAIR(NAME, __VA_ARGS__)
-
-DEFINE_PAIR_(im2col_maxpool, IM2COL_, MAXPOOL_)
-DEFINE_PAIR_(im2col_bnstats, IM2COL_, BNSTATS_)
-DEFINE_PAIR_(im2col_histc, IM2COL_, HISTC_)
-DEFINE_PAIR_(im2col_upsample, IM2COL_, UPSAMPLE_)
-DEFINE_PAIR_(maxpool_bnstats, MAXPOOL_, BNSTATS_)
-DEFINE_PAIR_(maxpool_upsample, MAXPOOL_, UPSAMPLE_)
-DEFINE_PAIR_(histc_maxpool, HISTC_, MAXPOOL_)
-DEFINE_PAIR_(histc_upsample, HISTC_, UPSAMPLE_)
-DEFINE_PAIR_(upsample_bnstats, UPSAMPLE_, BNSTATS_)
-DEFINE_PAIR_(histc_bnstats, HISTC_, BNSTATS_)
 
 }  // extern "C"
 

@@ -1,0 +1,4 @@
+// Fused pair im2col_upsample: one translation unit per pair so that the variants compile in parallel.
+#include "dl_host.cuh"
+
+DEFINE_PAIR_(im2col_upsample, IM2COL_, UPSAMPLE_)
