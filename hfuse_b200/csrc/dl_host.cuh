@@ -76,7 +76,7 @@ int prep_bnstats(HFUSE_BNSTATS_PARAMS(), BnStatsArgs& a) {
     a.total = (float)((double)N * (double)HW);
     a.mean = mean; a.invstd = invstd; a.moments = moments;
     a.partial = nullptr; a.tickets = nullptr;
-    a.S = 1; a.ips = N;
+    a.S = 1; a.chunk = 0; a.per_channel = 0;
     a.vec = (HW % 4) == 0;
     a.ws = workspace; a.ws_bytes = workspace_bytes;
     return HFUSE_OK;
@@ -98,6 +98,8 @@ int prep_upsample(HFUSE_UPSAMPLE_PARAMS(), UpsampleArgs& a) {
     a.align_corners = align_corners ? 1 : 0;
     const long long items = (long long)N * C * outH * (outW / 4);
     a.mode = ((outW % 4) == 0 && items <= kMaxItems) ? 1 : 0;
+    const long long strips = (long long)N * C * (H + 1LL) * (W / 4);
+    if (!align_corners && outH == 2LL * H && outW == 2LL * W && (W % 4) == 0 && strips <= kMaxItems) a.mode = 2;
     return HFUSE_OK;
 }
 

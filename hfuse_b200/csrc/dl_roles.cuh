@@ -216,7 +216,8 @@ struct UpsampleArgs {
     int N, C, H, W, outH, outW;
     float rheight, rwidth;
     int align_corners;
-    int mode;   // 0 = one output per item, 1 = four adjacent outputs per item (outW % 4 == 0)
+    int mode;   // 0 = one output per item, 1 = four adjacent outputs per item (outW % 4 == 0),
+                // 2 = exact x2 strip path (run_x2)
 };
 
 __device__ __forceinline__ void bilinear_src(float scale, int dst, int align, int in_size, int& i1, int& i1p,
@@ -276,6 +277,74 @@ struct UpsampleRole {
         }
     }
 
+    // Exact x2, align_corners = false, W % 4 == 0.  The source weights are
+    // then exactly {0.25, 0.75} (1 and 0 on the clamped first row / column), so
+    // the generic formula can be evaluated from registers: one item = input
+    // columns 4m-1 .. 4m+4 of two neighbouring input rows (two 16-byte loads
+    // and four scalars) -> an 8-wide strip of the two output rows between them
+    // (four 16-byte stores).  Every product and sum is the one the generic
+    // path computes, so both paths give the same bits.
+    template <int T>
+    static __device__ __forceinline__ void run_x2(const Args& a, const RoleCtx& ctx) {
+        const unsigned W4 = (unsigned)a.W >> 2;
+        const unsigned J = (unsigned)a.H + 1;                        // row pairs per plane
+        const unsigned total = (unsigned)a.N * a.C * J * W4;         // host guarantees < 2^31
+        for (unsigned it = (unsigned)ctx.block * T + ctx.tid; it < total; it += (unsigned)ctx.nblocks * T) {
+            const unsigned m = it % W4;
+            const unsigned r = it / W4;
+            const int j = (int)(r % J);
+            const unsigned plane = r / J;
+            // output rows 2j-1 (if j >= 1) and 2j (if j <= H-1) blend input rows ra and rb
+            const int ra = j > 0 ? j - 1 : 0;
+            const int rb = j == 0 ? (a.H > 1 ? 1 : 0) : (j < a.H ? j : a.H - 1);
+            const float* pa = a.in + (size_t)plane * a.H * a.W + (size_t)ra * a.W + 4 * m;
+            const float* pb = a.in + (size_t)plane * a.H * a.W + (size_t)rb * a.W + 4 * m;
+            const bool has_l = m > 0, has_r = m + 1 < W4;
+            const float4 qa = __ldg(reinterpret_cast<const float4*>(pa));
+            const float4 qb = __ldg(reinterpret_cast<const float4*>(pb));
+            float ca[6], cb[6];          // columns 4m-1 .. 4m+4
+            ca[1] = qa.x; ca[2] = qa.y; ca[3] = qa.z; ca[4] = qa.w;
+            cb[1] = qb.x; cb[2] = qb.y; cb[3] = qb.z; cb[4] = qb.w;
+            ca[0] = has_l ? __ldg(pa - 1) : 0.f;  cb[0] = has_l ? __ldg(pb - 1) : 0.f;
+            ca[5] = has_r ? __ldg(pa + 4) : ca[4]; cb[5] = has_r ? __ldg(pb + 4) : cb[4];   // w1p = 0 at the edge
+            // horizontal blends of both input rows for output columns 8m .. 8m+7
+            float ta[8], tb[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                // even column 8m+2k: source 4m+k-0.25 -> (4m+k-1, 4m+k) with weights (0.25, 0.75);
+                // the very first column clamps to source 0 -> weights (1, 0) on columns (0, 1)
+                if (k == 0 && !has_l) {
+                    ta[0] = __fadd_rn(__fmul_rn(1.f, ca[1]), __fmul_rn(0.f, a.W > 1 ? ca[2] : ca[1]));
+                    tb[0] = __fadd_rn(__fmul_rn(1.f, cb[1]), __fmul_rn(0.f, a.W > 1 ? cb[2] : cb[1]));
+                } else {
+                    ta[2 * k] = __fadd_rn(__fmul_rn(0.25f, ca[k]), __fmul_rn(0.75f, ca[k + 1]));
+                    tb[2 * k] = __fadd_rn(__fmul_rn(0.25f, cb[k]), __fmul_rn(0.75f, cb[k + 1]));
+                }
+                // odd column 8m+2k+1: source 4m+k+0.25 -> (4m+k, 4m+k+1) with weights (0.75, 0.25)
+                ta[2 * k + 1] = __fadd_rn(__fmul_rn(0.75f, ca[k + 1]), __fmul_rn(0.25f, ca[k + 2]));
+                tb[2 * k + 1] = __fadd_rn(__fmul_rn(0.75f, cb[k + 1]), __fmul_rn(0.25f, cb[k + 2]));
+            }
+            float* orow = a.out + (size_t)plane * a.outH * a.outW + 8 * m;
+            if (j > 0) {        // odd output row 2j-1: weights (0.75, 0.25)
+                float o[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) o[k] = __fadd_rn(__fmul_rn(0.75f, ta[k]), __fmul_rn(0.25f, tb[k]));
+                float* p = orow + (size_t)(2 * j - 1) * a.outW;
+                stg_stream4(p, make_float4(o[0], o[1], o[2], o[3]));
+                stg_stream4(p + 4, make_float4(o[4], o[5], o[6], o[7]));
+            }
+            if (j < a.H) {      // even output row 2j: weights (0.25, 0.75), or (1, 0) on the clamped row 0
+                const float h0 = j == 0 ? 1.f : 0.25f, h1 = j == 0 ? 0.f : 0.75f;
+                float o[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) o[k] = __fadd_rn(__fmul_rn(h0, ta[k]), __fmul_rn(h1, tb[k]));
+                float* p = orow + (size_t)(2 * j) * a.outW;
+                stg_stream4(p, make_float4(o[0], o[1], o[2], o[3]));
+                stg_stream4(p + 4, make_float4(o[4], o[5], o[6], o[7]));
+            }
+        }
+    }
+
     template <int T>
     static __device__ __forceinline__ void run_scalar(const Args& a, const RoleCtx& ctx) {
         const unsigned long long total = (unsigned long long)a.N * a.C * a.outH * a.outW;
@@ -298,7 +367,8 @@ struct UpsampleRole {
 
     template <int T, int BAR>
     static __device__ __forceinline__ void run(const Args& a, const RoleCtx& ctx) {
-        if (a.mode == 1) run_vec4<T>(a, ctx);
+        if (a.mode == 2) run_x2<T>(a, ctx);
+        else if (a.mode == 1) run_vec4<T>(a, ctx);
         else run_scalar<T>(a, ctx);
     }
 };
@@ -372,6 +442,14 @@ struct HistcRole {
 // =============================================================================
 // batch_norm_collect_statistics: per-channel mean and 1/sqrt(biased var + eps)
 // =============================================================================
+// Work unit = (channel, slice): the channel's N*HW values, taken in (n, hw)
+// order, are cut into S equal slices and ONE WARP reduces one slice: each lane
+// accumulates shifted sums over its 16-byte loads, converts them to Welford
+// moments (count, mean, M2) and the warp folds them with a shuffle tree of
+// Chan merges.  With S > 1 the slice moments go to scratch and the warp that
+// takes the last ticket of a channel folds all S of them in slice order, so
+// the result does not depend on arrival order.  A warp never waits for
+// another one, so the role needs no barrier and no shared memory.
 struct BnStatsArgs {
     const float* x;       // [N][C][HW]
     int N, C, HW;
@@ -382,14 +460,15 @@ struct BnStatsArgs {
     double* moments;      // optional [C][3]: n, n*mean, M2 + n*mean^2 (summable across GPUs), or null
     float* partial;       // scratch [C][S][3], used when S > 1
     unsigned* tickets;    // scratch [C], zero before the first call; every call leaves it zero
-    int S;                // batch slices per channel (<= 32)
-    int ips;              // images per slice
+    int S;                // slices per channel (<= kBnMaxSlices)
+    unsigned chunk;       // vector (or scalar) items per slice
+    unsigned per_channel; // vector (or scalar) items per channel = N * HW / (vec ? 4 : 1)
     int vec;              // HW % 4 == 0: 16-byte loads
     size_t ws_bytes;      // size of the caller's scratch buffer (host-side check only)
     void* ws;             // the caller's scratch buffer
 };
 
-constexpr int kBnMaxSlices = 32;
+constexpr int kBnMaxSlices = 256;
 inline size_t bn_ticket_bytes(int C) { return (((size_t)C * sizeof(unsigned)) + 255) & ~(size_t)255; }
 inline size_t bn_workspace_bytes(int C) {
     return bn_ticket_bytes(C) + (size_t)C * kBnMaxSlices * 3 * sizeof(float);
@@ -401,7 +480,7 @@ __device__ __forceinline__ Moments chan_merge(Moments a, Moments b) {
     const float n = a.n + b.n;
     if (n == 0.f) return a;
     const float delta = b.mean - a.mean;
-    const float fb = b.n / n;
+    const float fb = __fdividef(b.n, n);
     Moments r;
     r.n = n;
     r.mean = a.mean + delta * fb;
@@ -425,21 +504,22 @@ __device__ __forceinline__ Moments warp_merge(Moments m) {
 
 struct BnStatsRole {
     using Args = BnStatsArgs;
-    // two parity buffers of per-warp moments
-    static int smem_bytes(const Args&, int T) { return 2 * 3 * (T / 32) * (int)sizeof(float); }
-    // Split each channel's batch into S slices so that the grid has a few units
-    // per block, without making a unit smaller than two loads per thread.
+    static int smem_bytes(const Args&, int) { return 0; }
+
+    // Slices per channel: about two units per resident warp, but never less
+    // than two loads per lane in a slice.
     static int plan(Args& a, int T, int grid) {
-        const long long per_img = a.vec ? a.HW / 4 : a.HW;
-        long long s_small = ((long long)a.N * per_img) / (2LL * T);
+        const long long per_channel = (long long)a.N * a.HW / (a.vec ? 4 : 1);
+        long long s_small = per_channel / 64;
         if (s_small < 1) s_small = 1;
-        if (s_small > a.N) s_small = a.N;
         if (s_small > kBnMaxSlices) s_small = kBnMaxSlices;
-        long long s_want = (4LL * grid + a.C - 1) / a.C;
+        const long long warps = (long long)grid * (T / 32);
+        long long s_want = (2 * warps + a.C - 1) / a.C;
         if (s_want < 1) s_want = 1;
-        long long S = s_want < s_small ? s_want : s_small;
-        a.ips = (int)((a.N + S - 1) / S);
-        a.S = (a.N + a.ips - 1) / a.ips;
+        const long long S = s_want < s_small ? s_want : s_small;
+        a.per_channel = (unsigned)per_channel;
+        a.chunk = (unsigned)((per_channel + S - 1) / S);
+        a.S = (int)((per_channel + a.chunk - 1) / a.chunk);
         if (a.S > 1) {
             if (a.ws == nullptr || a.ws_bytes < bn_workspace_bytes(a.C)) return -4;   // HFUSE_ERR_WORKSPACE
             a.tickets = reinterpret_cast<unsigned*>(a.ws);
@@ -463,92 +543,93 @@ struct BnStatsRole {
     template <int T, int BAR>
     static __device__ __forceinline__ void run(const Args& a, const RoleCtx& ctx) {
         constexpr int NW = T / 32;
-        static_assert(NW <= 32, "one warp merges the per-warp moments");
-        float* sh = reinterpret_cast<float*>(ctx.smem);
-        const int lane = ctx.tid & 31, warp = ctx.tid >> 5;
-        const int units = a.C * a.S;
-        int parity = 0;
-        for (int u = ctx.block; u < units; u += ctx.nblocks, parity ^= 1) {
-            const int c = u / a.S, s = u % a.S;
-            const int n0 = s * a.ips, n1 = min(a.N, n0 + a.ips);
-            // ---- per-thread Welford, four independent lanes sharing one count
-            float cnt = 0.f;
-            float mu[4] = {0.f, 0.f, 0.f, 0.f}, m2[4] = {0.f, 0.f, 0.f, 0.f};
-            float tail_n = 0.f;
-            if (a.vec) {
-                const int hw4 = a.HW >> 2;
-                const int total = (n1 - n0) * hw4;
-                for (int k = ctx.tid; k < total; k += T) {
-                    const int n = n0 + k / hw4, off = k % hw4;
-                    const float4 v = ldg_stream4(a.x + ((size_t)n * a.C + c) * a.HW + 4 * off);
-                    cnt += 1.f;
-                    const float r = __frcp_rn(cnt);
-                    const float xs[4] = {v.x, v.y, v.z, v.w};
+        constexpr int UNROLL = 4;
+        const int lane = ctx.tid & 31;
+        const unsigned units = (unsigned)a.C * (unsigned)a.S;
+        const unsigned per_img = a.vec ? (unsigned)a.HW >> 2 : (unsigned)a.HW;
+        for (unsigned u = (unsigned)ctx.block * NW + (ctx.tid >> 5); u < units; u += (unsigned)ctx.nblocks * NW) {
+            const unsigned c = u / a.S, s = u - c * a.S;
+            const unsigned k0 = s * a.chunk;
+            const unsigned k1 = min(k0 + a.chunk, a.per_channel);
+            // ---- per-lane sums of (x - shift) and (x - shift)^2; shift = the lane's first value
+            float cnt = 0.f, sum = 0.f, sq = 0.f, shift = 0.f;
+            for (unsigned k = k0 + lane; k < k1; k += 32 * UNROLL) {
+                if (a.vec) {
+                    float4 v[UNROLL];
+                    bool ok[UNROLL];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float d = xs[j] - mu[j];
-                        mu[j] += d * r;
-                        m2[j] += d * (xs[j] - mu[j]);
+                    for (int j = 0; j < UNROLL; ++j) {
+                        const unsigned kk = k + 32 * j;
+                        ok[j] = kk < k1;
+                        if (ok[j]) {
+                            const unsigned n = kk / per_img, off = kk - n * per_img;
+                            v[j] = ldg_stream4(a.x + ((size_t)n * a.C + c) * a.HW + 4 * off);
+                        }
                     }
-                }
-            } else {
-                const int total = (n1 - n0) * a.HW;
-                for (int k = ctx.tid; k < total; k += T) {
-                    const int n = n0 + k / a.HW, off = k % a.HW;
-                    const float xv = __ldg(a.x + ((size_t)n * a.C + c) * a.HW + off);
-                    tail_n += 1.f;
-                    const float d = xv - mu[0];
-                    mu[0] += d * __frcp_rn(tail_n);
-                    m2[0] += d * (xv - mu[0]);
-                }
-            }
-            Moments m;
-            if (a.vec) {
-                Moments q0{cnt, mu[0], m2[0]}, q1{cnt, mu[1], m2[1]}, q2{cnt, mu[2], m2[2]}, q3{cnt, mu[3], m2[3]};
-                m = chan_merge(chan_merge(q0, q1), chan_merge(q2, q3));
-            } else {
-                m = Moments{tail_n, mu[0], m2[0]};
-            }
-            // ---- warp, then role-wide merge through shared memory and the role's barrier
-            m = warp_merge(m);
-            float* buf = sh + parity * 3 * NW;
-            if (lane == 0) { buf[warp] = m.n; buf[NW + warp] = m.mean; buf[2 * NW + warp] = m.m2; }
-            role_sync<BAR, T>();
-            if (warp == 0) {
-                Moments w = (lane < NW) ? Moments{buf[lane], buf[NW + lane], buf[2 * NW + lane]}
-                                        : Moments{0.f, 0.f, 0.f};
-                w = warp_merge(w);
-                if (a.S == 1) {
-                    if (lane == 0) finish(a, c, w);
+#pragma unroll
+                    for (int j = 0; j < UNROLL; ++j) {
+                        if (!ok[j]) continue;
+                        if (cnt == 0.f) shift = v[j].x;
+                        const float d0 = v[j].x - shift, d1 = v[j].y - shift, d2 = v[j].z - shift, d3 = v[j].w - shift;
+                        sum += (d0 + d1) + (d2 + d3);
+                        sq = fmaf(d0, d0, fmaf(d1, d1, fmaf(d2, d2, fmaf(d3, d3, sq))));
+                        cnt += 4.f;
+                    }
                 } else {
-                    // publish this slice, then the last slice to arrive folds all of
-                    // them in slice order (so the result does not depend on timing)
-                    unsigned ticket = 0;
-                    if (lane == 0) {
-                        float* p = a.partial + ((size_t)c * a.S + s) * 3;
-                        __stcg(p, w.n); __stcg(p + 1, w.mean); __stcg(p + 2, w.m2);
-                        __threadfence();
-                        ticket = atomicAdd(a.tickets + c, 1u);
+                    float v[UNROLL];
+                    bool ok[UNROLL];
+#pragma unroll
+                    for (int j = 0; j < UNROLL; ++j) {
+                        const unsigned kk = k + 32 * j;
+                        ok[j] = kk < k1;
+                        if (ok[j]) {
+                            const unsigned n = kk / per_img, off = kk - n * per_img;
+                            v[j] = __ldg(a.x + ((size_t)n * a.C + c) * a.HW + off);
+                        }
                     }
-                    ticket = __shfl_sync(0xffffffffu, ticket, 0);
-                    if (ticket == (unsigned)(a.S - 1)) {
-                        __threadfence();
-                        Moments q{0.f, 0.f, 0.f};
-                        if (lane < a.S) {
-                            const float* p = a.partial + ((size_t)c * a.S + lane) * 3;
-                            q = Moments{__ldcg(p), __ldcg(p + 1), __ldcg(p + 2)};
-                        }
-                        q = warp_merge(q);
-                        if (lane == 0) {
-                            finish(a, c, q);
-                            a.tickets[c] = 0u;     // ready for the next call
-                        }
+#pragma unroll
+                    for (int j = 0; j < UNROLL; ++j) {
+                        if (!ok[j]) continue;
+                        if (cnt == 0.f) shift = v[j];
+                        const float d = v[j] - shift;
+                        sum += d;
+                        sq = fmaf(d, d, sq);
+                        cnt += 1.f;
                     }
                 }
             }
-            // the parity buffer keeps warp 0's reads of this unit apart from
-            // the next unit's writes; the unit after that is fenced by the
-            // next role barrier
+            Moments m{0.f, 0.f, 0.f};
+            if (cnt > 0.f) {
+                const float dm = sum / cnt;
+                m = Moments{cnt, shift + dm, fmaxf(sq - sum * dm, 0.f)};
+            }
+            m = warp_merge(m);
+            if (a.S == 1) {
+                if (lane == 0) finish(a, (int)c, m);
+                continue;
+            }
+            // publish this slice; the warp that takes the last ticket folds all slices
+            unsigned ticket = 0;
+            if (lane == 0) {
+                float* p = a.partial + ((size_t)c * a.S + s) * 3;
+                __stcg(p, m.n); __stcg(p + 1, m.mean); __stcg(p + 2, m.m2);
+                __threadfence();
+                ticket = atomicAdd(a.tickets + c, 1u);
+            }
+            ticket = __shfl_sync(0xffffffffu, ticket, 0);
+            if (ticket == (unsigned)(a.S - 1)) {
+                __threadfence();
+                Moments q{0.f, 0.f, 0.f};
+                for (int i = lane; i < a.S; i += 32) {      // fixed order: lane, lane+32, ...
+                    const float* p = a.partial + ((size_t)c * a.S + i) * 3;
+                    q = chan_merge(q, Moments{__ldcg(p), __ldcg(p + 1), __ldcg(p + 2)});
+                }
+                q = warp_merge(q);
+                if (lane == 0) {
+                    finish(a, (int)c, q);
+                    a.tickets[c] = 0u;     // ready for the next call
+                }
+            }
         }
     }
 };

@@ -1,0 +1,74 @@
+"""The C-ABI library loads without a GPU and exports every symbol the public header declares."""
+import ctypes
+import os
+import re
+
+import numpy as np
+
+from conftest import ROOT
+from hfuse_b200 import _lib
+
+
+def _declared_in_header():
+    text = open(os.path.join(ROOT, "include", "hfuse_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"HFUSE_API\s+[\w\s\*]+?\b(hfuse_\w+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported():
+    declared = _declared_in_header()
+    assert len(declared) >= 30
+    L = ctypes.CDLL(_lib.LIB_PATH)
+    for name in declared:
+        assert hasattr(L, name), name
+    assert sorted(_lib.exported_symbols()) == declared
+
+
+def test_error_strings_and_version():
+    assert _lib.lib().hfuse_version() >= 100
+    assert _lib.error_string(0) == "ok"
+    assert "aligned" in _lib.error_string(-2)
+
+
+def test_tuning_table():
+    for name in list(_lib.DL_SOLO) + list(_lib.DL_PAIRS) + list(_lib.CRYPTO_SOLO) + list(_lib.CRYPTO_PAIRS):
+        v = _lib.tune_variants(name)
+        assert len(v) >= 5
+        for d in v:
+            t1, t2, mb = (int(x) for x in d.split(":"))
+            assert t1 % 128 == 0 and t2 % 128 == 0 and mb >= 1      # 128-thread steps, as in the reference sweep
+    assert _lib.lib().hfuse_tune_set(b"no_such_pair", 0, 0) == -7
+    assert _lib.lib().hfuse_tune_set(b"im2col_maxpool", 999, 0) < 0
+    _lib.tune_set("im2col_maxpool", 1, 2)
+    _lib.tune_set("im2col_maxpool", -1, 0)
+
+
+def test_bad_arguments_are_rejected_before_any_launch():
+    L = _lib.lib()
+    # null pointers / bad shapes: checked on the host, so no GPU is needed
+    assert L.hfuse_im2col_f32(None, 1, 1, 4, 4, 3, 3, 1, 1, 1, 1, 1, 1, None, None) == -1
+    assert L.hfuse_im2col_f32(16, 1, 1, 4, 4, 9, 9, 0, 0, 1, 1, 1, 1, 16, None) == -1      # kernel too large
+    assert L.hfuse_im2col_f32(20, 1, 1, 4, 4, 3, 3, 1, 1, 1, 1, 1, 1, 16, None) == -2      # misaligned
+    assert L.hfuse_histc_f32(16, 8, 4, 1.0, 1.0, 16, None) == -1                           # empty range
+    assert L.hfuse_maxpool2d_f32(16, 1, 1, 4, 4, 9, 9, 2, 2, 2, 2, 0, 0, 1, 1, 16, 16, None) == -1
+    assert L.hfuse_bnstats_f32(16, 0, 1, 1, 1e-5, 16, 16, None, None, 0, None) == -1
+    tgt = bytes(32)
+    assert L.hfuse_sha256d_search(bytes(80), 0, (1 << 32) + 1, tgt, 16, None) == -3        # beyond the nonce space
+    assert L.hfuse_ethash_search(None, 0, bytes(32), 0, 1, tgt, 16, None) == -1
+
+
+def test_host_generator_matches_oracle():
+    from hfuse_b200 import workloads
+    from oracle import crypto as OC
+    assert np.array_equal(workloads.xoshiro_bytes(3, 4097), OC.xoshiro_bytes(3, 4097))
+    c3 = workloads.config3()
+    assert len(c3["blake_header"]) == 80 and len(c3["sha_header"]) == 80
+    assert int.from_bytes(c3["target"], "big") == 2 ** 224
+
+
+def test_ops_refuse_cpu_tensors():
+    import pytest
+    import torch
+    from hfuse_b200 import ops
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.im2col(torch.zeros(1, 1, 4, 4), 3, 1)

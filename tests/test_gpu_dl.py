@@ -1,0 +1,207 @@
+"""GPU parity of the five DL kernels through the C ABI: golden fixtures, the oracle on
+seeded inputs, edge cases, and the benchmark configurations at full size."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN
+from hfuse_b200 import _lib, ops, workloads
+from oracle import dl
+
+sys.path.insert(0, GOLDEN)
+from make_golden import HIST_CASES, IM2COL_CASES, POOL_CASES, UP_CASES  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gold():
+    return np.load(os.path.join(GOLDEN, "dl_small.npz"))
+
+
+def _u32(t):
+    return t.cpu().numpy().view(np.uint32)
+
+
+def test_golden_im2col(dev, gold):
+    x = torch.from_numpy(gold["im2col_x"]).to(dev)
+    for i, (kh, kw, ph, pw, sh, sw, dh, dw) in enumerate(IM2COL_CASES):
+        out = ops.im2col(x, (kh, kw), (ph, pw), (sh, sw), (dh, dw))
+        assert np.array_equal(out.cpu().numpy(), gold[f"im2col_{i}"])
+
+
+def test_golden_maxpool(dev, gold):
+    x = torch.from_numpy(gold["pool_x"]).to(dev)
+    for i, (kh, kw, sh, sw, ph, pw, dh, dw) in enumerate(POOL_CASES):
+        v, ix = ops.max_pool2d_with_indices(x, (kh, kw), (sh, sw), (ph, pw), (dh, dw))
+        assert np.array_equal(v.cpu().numpy(), gold[f"pool_v_{i}"], equal_nan=True)
+        assert np.array_equal(ix.cpu().numpy(), gold[f"pool_i_{i}"])
+
+
+def test_golden_bnstats(dev, gold):
+    m, s = ops.batch_norm_stats(torch.from_numpy(gold["bn_x"]).to(dev), 1e-5)
+    np.testing.assert_allclose(m.cpu().numpy(), gold["bn_mean"], rtol=1e-5)      # tolerance of the benchmark spec
+    np.testing.assert_allclose(s.cpu().numpy(), gold["bn_invstd"], rtol=1e-5)
+
+
+def test_golden_upsample(dev, gold):
+    x = torch.from_numpy(gold["up_x"]).to(dev)
+    for i, (oh, ow, ac) in enumerate(UP_CASES):
+        out = ops.upsample_bilinear2d(x, (oh, ow), align_corners=ac)
+        assert np.array_equal(out.cpu().numpy(), gold[f"up_{i}"])                # same roundings as the restatement
+
+
+def test_golden_histc(dev, gold):
+    x = torch.from_numpy(gold["hist_x"]).to(dev)
+    for i, (nb, lo, hi) in enumerate(HIST_CASES):
+        assert np.array_equal(_u32(ops.histc(x, nb, lo, hi)), gold[f"hist_{i}"])
+
+
+@pytest.mark.parametrize("shape,prm", [
+    ((2, 3, 12, 16), (3, 3, 1, 1, 1, 1, 1, 1)),      # tile path, small
+    ((1, 1, 3, 4), (3, 3, 1, 1, 1, 1, 1, 1)),        # tile path, single strip per row
+    ((2, 2, 10, 8), (3, 3, 2, 2, 1, 1, 1, 1)),       # tile path with pad 2 (scalar loads)
+    ((2, 2, 10, 10), (3, 3, 0, 0, 1, 1, 1, 1)),      # tile path without padding
+    ((1, 2, 9, 11), (5, 2, 2, 1, 2, 3, 1, 2)),       # generic path
+    ((3, 1, 1, 1), (1, 1, 0, 0, 1, 1, 1, 1)),        # 1x1
+])
+def test_im2col_shapes(dev, shape, prm):
+    g = torch.Generator().manual_seed(11)
+    x = torch.rand(*shape, generator=g) * 2 - 1
+    kh, kw, ph, pw, sh, sw, dh, dw = prm
+    out = ops.im2col(x.to(dev), (kh, kw), (ph, pw), (sh, sw), (dh, dw))
+    assert torch.equal(out.cpu(), dl.im2col_torch(x, *prm))
+
+
+@pytest.mark.parametrize("shape,prm", [
+    ((2, 3, 8, 16), (2, 2, 2, 2, 0, 0, 1, 1)),       # 2x2/2 path
+    ((1, 1, 2, 8), (2, 2, 2, 2, 0, 0, 1, 1)),        # 2x2/2 path, one output row
+    ((2, 3, 9, 10), (2, 2, 2, 2, 0, 0, 1, 1)),       # generic (odd sizes, last row/col dropped)
+    ((2, 3, 9, 10), (3, 3, 2, 1, 1, 1, 1, 1)),
+    ((1, 2, 7, 7), (3, 2, 1, 2, 1, 1, 2, 2)),
+])
+def test_maxpool_shapes_with_ties_and_nan(dev, shape, prm):
+    g = torch.Generator().manual_seed(12)
+    x = torch.randint(0, 3, shape, generator=g).float()       # plenty of exact ties
+    x.view(-1)[5] = float("nan")
+    x[0, 0, 0] = -float("inf")
+    kh, kw, sh, sw, ph, pw, dh, dw = prm
+    v, ix = ops.max_pool2d_with_indices(x.to(dev), (kh, kw), (sh, sw), (ph, pw), (dh, dw))
+    vr, ir = dl.maxpool_torch(x, *prm)
+    assert np.array_equal(v.cpu().numpy(), vr.numpy(), equal_nan=True)
+    assert torch.equal(ix.cpu(), ir)
+
+
+@pytest.mark.parametrize("shape", [(3, 5, 7, 9), (1, 4, 1, 1), (64, 3, 5, 4), (5, 2, 3, 3), (2, 3, 128, 128),
+                                   (1, 1, 1, 2), (7, 300, 2, 2)])
+def test_bnstats_shapes(dev, shape):
+    g = torch.Generator().manual_seed(13)
+    x = torch.randn(*shape, generator=g) * 3 + 10           # mean far from zero: cancellation would show
+    m, s = ops.batch_norm_stats(x.to(dev), 1e-5)
+    mr, sr = dl.bnstats_f64(x, 1e-5)
+    np.testing.assert_allclose(m.cpu().double().numpy(), mr.numpy(), rtol=1e-5)
+    np.testing.assert_allclose(s.cpu().double().numpy(), sr.numpy(), rtol=1e-5)
+    # calling again with the same workspace gives the same answer (the scratch cleans itself)
+    m2, s2 = ops.batch_norm_stats(x.to(dev), 1e-5)
+    assert torch.equal(m, m2) and torch.equal(s, s2)
+
+
+def test_bnstats_moments_sum_like_the_allreduce(dev):
+    from hfuse_b200 import sharding
+    g = torch.Generator().manual_seed(14)
+    x = 0.5 + 2.0 * torch.randn(8, 16, 6, 6, generator=g)
+    parts = []
+    for r in range(4):
+        op = ops.BnStats(sharding.shard_batch(x, r, 4).contiguous().to(dev), 1e-5, want_moments=True)
+        ops.run(op)
+        parts.append(op.moments)
+    total = torch.stack(parts).sum(0).contiguous()
+    mean, invstd = ops.bn_finalize(total, 1e-5)
+    mr, sr = dl.bnstats_f64(x, 1e-5)
+    np.testing.assert_allclose(mean.cpu().double().numpy(), mr.numpy(), rtol=1e-5)
+    np.testing.assert_allclose(invstd.cpu().double().numpy(), sr.numpy(), rtol=1e-5)
+
+
+@pytest.mark.parametrize("H,W,oh,ow,ac", [(7, 9, 14, 18, False), (7, 9, 14, 18, True), (7, 9, 10, 13, False),
+                                          (7, 9, 5, 20, True), (4, 4, 8, 8, False), (1, 4, 2, 8, False),
+                                          (6, 8, 12, 16, False), (5, 12, 10, 24, False), (3, 8, 3, 8, False)])
+def test_upsample_shapes(dev, H, W, oh, ow, ac):
+    g = torch.Generator().manual_seed(15)
+    x = torch.rand(2, 3, H, W, generator=g)
+    out = ops.upsample_bilinear2d(x.to(dev), (oh, ow), align_corners=ac).cpu().numpy()
+    assert np.array_equal(out, dl.upsample_numpy(x.numpy(), oh, ow, ac))
+    np.testing.assert_allclose(out, dl.upsample_torch(x, oh, ow, ac).numpy(), rtol=1e-5, atol=1e-6)
+
+
+def test_upsample_x2_strip_path_equals_generic_formula_with_nonfinite(dev):
+    # inf / nan must propagate exactly as in the per-output formula (0 * inf = nan)
+    x = torch.rand(1, 2, 6, 8)
+    x[0, 0, 1, 1] = float("inf")
+    x[0, 1, 0, 1] = float("nan")
+    x[0, 1, 5, 7] = -float("inf")
+    out = ops.upsample_bilinear2d(x.to(dev), scale_factor=2).cpu().numpy()
+    with np.errstate(invalid="ignore"):
+        ref = dl.upsample_numpy(x.numpy(), 12, 16)
+    assert np.array_equal(out, ref, equal_nan=True)
+
+
+@pytest.mark.parametrize("n,nb,lo,hi", [(1000, 10, -1.0, 1.0), (12345, 100, -3.0, 2.5), (7, 5, 0.0, 1.0),
+                                        (100003, 5000, -2.0, 2.0), (4096, 1, -10.0, 10.0), (0, 8, 0.0, 1.0),
+                                        (3, 4, 0.0, 1.0), (50001, 20000, -1.0, 1.0)])
+def test_histc_shapes(dev, n, nb, lo, hi):
+    g = torch.Generator().manual_seed(16)
+    x = torch.randn(n, generator=g)
+    if n >= 3:
+        x[0], x[1], x[2] = hi, lo, float("nan")
+    got = _u32(ops.histc(x.to(dev), nb, lo, hi)) if n else _u32(ops.run(ops.Histc(torch.empty(0, device=dev), nb, lo, hi)))
+    assert np.array_equal(got, dl.histc_numpy(x.numpy(), nb, lo, hi))
+
+
+def test_full_size_configurations(dev):
+    w = workloads.config0()
+    col = ops.im2col(w["im"].to(dev), **w["im2col"])
+    assert torch.equal(col.cpu(), dl.im2col_torch(w["im"], 3, 3, 1, 1, 1, 1, 1, 1))
+    v, ix = ops.max_pool2d_with_indices(w["pool"].to(dev), **w["maxpool"])
+    vr, ir = dl.maxpool_torch(w["pool"], 2, 2, 2, 2, 0, 0, 1, 1)
+    assert torch.equal(v.cpu(), vr) and torch.equal(ix.cpu(), ir)
+    del col
+    w = workloads.config1()
+    m, s = ops.batch_norm_stats(w["bn"].to(dev), w["eps"])
+    mr, sr = dl.bnstats_f64(w["bn"], w["eps"])
+    np.testing.assert_allclose(m.cpu().double().numpy(), mr.numpy(), rtol=1e-5)
+    np.testing.assert_allclose(s.cpu().double().numpy(), sr.numpy(), rtol=1e-5)
+    up = ops.upsample_bilinear2d(w["up"].to(dev), scale_factor=2).cpu()
+    ref = dl.upsample_torch(w["up"], 112, 112)
+    assert ((up - ref).abs() <= 1e-6 * ref.abs()).all()                       # 1e-6 relative, as specified
+    w = workloads.config2()
+    cnt = ops.histc(w["hist"].to(dev), w["bins"], w["lo"], w["hi"])
+    ref = dl.histc_torch(w["hist"], 256, -4, 4)
+    assert np.array_equal(_u32(cnt), ref)
+    assert int(ref.sum()) + int(((w["hist"] < -4) | (w["hist"] > 4)).sum()) == w["hist"].numel()
+
+
+def test_every_standalone_variant_gives_the_same_bytes(dev):
+    g = torch.Generator().manual_seed(17)
+    x = (torch.rand(2, 4, 16, 16, generator=g) * 2 - 1).to(dev)
+    base = ops.im2col(x, 3, 1, 1, 1)
+    for v in range(len(_lib.tune_variants("im2col"))):
+        _lib.tune_set("im2col", v, 0)
+        try:
+            assert torch.equal(ops.im2col(x, 3, 1, 1, 1), base)
+        finally:
+            _lib.tune_set("im2col", -1, 0)
+
+
+def test_error_codes_on_device_buffers(dev):
+    x = torch.zeros(1, 1, 4, 4, device=dev)
+    with pytest.raises(ValueError):
+        ops.im2col(x, 9, 0)
+    with pytest.raises(_lib.HfuseError) as e:
+        op = ops.BnStats(torch.zeros(64, 4, 64, 64, device=dev), workspace=torch.zeros(16, dtype=torch.uint8, device=dev))
+        ops.run(op)
+    assert e.value.code == -4
+    with pytest.raises(ValueError):
+        ops.Histc(x, 4, 2.0, 1.0)
