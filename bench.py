@@ -284,6 +284,8 @@ def run_ours(args):
 
     if args.only:
         return run_only(args, torch, ops, crypto, workloads, dev)
+    if args.tune:
+        return run_tune(args, torch, ops, crypto, workloads, dev)
 
     NSETS = 6
     name, sets, nbytes = build_dl_sets(torch, ops, workloads, 1, dev, NSETS)
@@ -460,6 +462,93 @@ def run_only(args, torch, ops, crypto, workloads, dev):
     print(json.dumps({"only": args.only, "mode": args.mode, "count": count, "ms_per_step": round(ms, 3)}))
 
 
+def run_tune(args, torch, ops, crypto, workloads, dev):
+    """Sweep every compiled (T1, T2, blocks/SM) variant of every kernel and pair on the
+    benchmark workloads and print the fastest per name as JSON (the reference's split /
+    register-cap sweep, tools/llvm-smart-fuser/main.cpp:215-236 and
+    scripts/profile_and_collect_data.py:40-57, done at run time instead of by recompiling).
+    hfuse_b200/apply_tuning.py writes the result into the *_tuned.inc defaults."""
+    from hfuse_b200 import _lib
+    NS = 4
+    w0, w1, w2 = workloads.config0(), workloads.config1(), workloads.config2()
+
+    def mk(key, big_im2col=False):
+        if key == "im2col":
+            return ops.Im2col((w2 if big_im2col else w0)["im"].to(dev), **w0["im2col"])
+        if key == "maxpool":
+            return ops.MaxPool(w0["pool"].to(dev), **w0["maxpool"])
+        if key == "bnstats":
+            return ops.BnStats(w1["bn"].to(dev), w1["eps"])
+        if key == "upsample":
+            return ops.Upsample(w1["up"].to(dev), scale_factor=2)
+        return ops.Histc(w2["hist"].to(dev), w2["bins"], w2["lo"], w2["hi"])
+
+    result = {"solo": {}, "pair": {}}
+    steps = 48
+    for key in _lib.DL_SOLO:
+        sets = [mk(key) for _ in range(NS)]
+        times = {}
+        for v, d in enumerate(_lib.tune_variants(key)):
+            _lib.tune_set(key, v, 0)
+            times[d] = round(graph_region(torch, lambda i: ops.run(sets[i % NS]), NS, steps, 3) * 1e3, 2)
+        best = min(times, key=times.get)
+        _lib.tune_set(key, list(times).index(best), 0)       # keep the best standalone for the b2b baseline
+        result["solo"][key] = {"best": list(times).index(best), "variant": best, "us": times[best], "all": times}
+        del sets
+        torch.cuda.empty_cache()
+    for name, (ka, kb) in _lib.DL_PAIRS.items():
+        big = name == "im2col_histc"
+        sets = [(mk(ka, big), mk(kb, big)) for _ in range(NS)]
+        t_b2b = graph_region(torch, lambda i: ops.run_back_to_back(*sets[i % NS]), NS, steps, 3) * 1e3
+        times = {}
+        for v, d in enumerate(_lib.tune_variants(name)):
+            _lib.tune_set(name, v, 0)
+            times[d] = round(graph_region(torch, lambda i: ops.run_pair(*sets[i % NS]), NS, steps, 3) * 1e3, 2)
+        _lib.tune_set(name, -1, 0)
+        best = min(times, key=times.get)
+        result["pair"][name] = {"best": list(times).index(best), "variant": best, "us": times[best],
+                                "back_to_back_us": round(t_b2b, 2), "speedup": round(t_b2b / times[best], 3),
+                                "all": times}
+        del sets
+        torch.cuda.empty_cache()
+    # crypto: reduced sweeps (2^27 nonces for the ALU hashes, 2^23 for ethash)
+    c3, c4 = workloads.config3(), workloads.config4(dev)
+    NA, NE = 1 << 27, 1 << 23
+
+    def mkc(key):
+        if key == "blake256":
+            return crypto.Blake256(c3["blake_header"], 0, NA, c3["target"])
+        if key == "sha256d":
+            return crypto.Sha256d(c3["sha_header"], 0, NA, c3["target"])
+        if key == "sia":
+            return crypto.Sia(c4["sia_header"], 0, NA, c4["target"])
+        return crypto.Ethash(c4["dag"], c4["header_hash"], 0, NE, c4["target"])
+
+    none = lambda: None
+    for key in _lib.CRYPTO_SOLO:
+        sobj = mkc(key)
+        times = {}
+        for v, d in enumerate(_lib.tune_variants(key)):
+            _lib.tune_set(key, v, 0)
+            times[d] = round(time_region(torch, lambda i: crypto.run(sobj), 2, 1, none) / 2, 3)
+        best = min(times, key=times.get)
+        _lib.tune_set(key, list(times).index(best), 0)
+        result["solo"][key] = {"best": list(times).index(best), "variant": best, "ms": times[best], "all": times}
+    for name, (ka, kb) in _lib.CRYPTO_PAIRS.items():
+        a, b = mkc(ka), mkc(kb)
+        t_b2b = time_region(torch, lambda i: crypto.run_back_to_back(a, b), 2, 1, none) / 2
+        times = {}
+        for v, d in enumerate(_lib.tune_variants(name)):
+            _lib.tune_set(name, v, 0)
+            times[d] = round(time_region(torch, lambda i: crypto.run_pair(a, b), 2, 1, none) / 2, 3)
+        _lib.tune_set(name, -1, 0)
+        best = min(times, key=times.get)
+        result["pair"][name] = {"best": list(times).index(best), "variant": best, "ms": times[best],
+                                "back_to_back_ms": round(t_b2b, 3), "speedup": round(t_b2b / times[best], 3),
+                                "all": times}
+    print(json.dumps(result))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -471,6 +560,7 @@ def main():
     ap.add_argument("--count", type=int, default=1 << 24, help="nonces per step with --only cfg3|cfg4")
     ap.add_argument("--dag-items", type=int, default=8_388_608)
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--tune", action="store_true", help="sweep all variants and print the best per kernel / pair")
     ap.add_argument("--graph", action="store_true", help="with --only: replay the launches from a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":

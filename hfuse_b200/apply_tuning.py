@@ -1,0 +1,43 @@
+"""Writes the result of `python bench.py --tune` into the compiled defaults.
+
+    python bench.py --tune > tune.json          (on a B200)
+    python -m hfuse_b200.apply_tuning tune.json (anywhere; then rebuild)
+
+The reference picks the split and register cap of each pair by rebuilding and
+profiling every candidate (scripts/profile_and_collect_data.py:40-57); here all
+candidates are compiled in, the sweep runs once, and only the default index per
+kernel / pair changes.
+"""
+from __future__ import annotations
+
+import json
+import os
+import re
+import sys
+
+from . import _lib
+
+CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
+
+
+def apply(path: str) -> None:
+    with open(path) as f:
+        text = f.read()
+    res = json.loads(text[text.index("{"):])
+    for inc, solos, pairs in (("dl_tuned.inc", _lib.DL_SOLO, _lib.DL_PAIRS),
+                              ("crypto_tuned.inc", _lib.CRYPTO_SOLO, _lib.CRYPTO_PAIRS)):
+        p = os.path.join(CSRC, inc)
+        src = open(p).read()
+        for kind, names in (("Solo", solos), ("Pair", pairs)):
+            for name in names:
+                entry = res["solo" if kind == "Solo" else "pair"].get(name)
+                if entry is None:
+                    continue
+                src, n = re.subn(rf"(kDefault{kind}_{name} = )\d+;", rf"\g<1>{entry['best']};", src)
+                assert n == 1, name
+        open(p, "w").write(src)
+        print("updated", p)
+
+
+if __name__ == "__main__":
+    apply(sys.argv[1])

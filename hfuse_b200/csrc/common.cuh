@@ -46,6 +46,29 @@ __device__ __forceinline__ void stg_stream_2xi64(long long* p, long long a, long
     asm volatile("st.global.cs.v2.s64 [%0], {%1,%2};" ::"l"(p), "l"(a), "l"(b) : "memory");
 }
 
+// ---- division by a launch-time constant --------------------------------------------------
+// q = n / d for n < 2^31 as one multiply-high, one add and one shift
+// (m = floor(2^32 * (2^s - d) / d) + 1, s = ceil(log2 d); the sum cannot overflow for n < 2^31).
+struct FastDiv {
+    uint32_t d, m, s;
+};
+inline FastDiv make_fastdiv(uint32_t d) {
+    FastDiv f;
+    f.d = d;
+    uint32_t s = 0;
+    while ((1ull << s) < d) ++s;
+    f.s = s;
+    f.m = (uint32_t)((((1ull << 32) * ((1ull << s) - d)) / d) + 1);
+    return f;
+}
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, const FastDiv& f) { return (__umulhi(n, f.m) + n) >> f.s; }
+// n -> (n / d, n % d)
+__device__ __forceinline__ uint32_t fast_divmod(uint32_t n, const FastDiv& f, uint32_t& rem) {
+    const uint32_t q = fast_div(n, f);
+    rem = n - q * f.d;
+    return q;
+}
+
 // ---- role context ----------------------------------------------------------------
 // What a role body sees instead of threadIdx / blockDim: its own thread id
 // inside the range and the range size T (a compile-time constant).  blockIdx

@@ -43,6 +43,8 @@ int prep_im2col(HFUSE_IM2COL_PARAMS(), Im2colArgs& a) {
     a.mode = (kh == 3 && kw == 3 && sh == 1 && sw == 1 && dh == 1 && dw == 1 && (Wc % 4) == 0 && items > 0 &&
               items <= kMaxItems)
                  ? 1 : 0;
+    a.div_w4 = make_fastdiv(a.mode == 1 ? (uint32_t)(Wc / 4) : 1u);
+    a.div_hc = make_fastdiv((uint32_t)Hc);
     return HFUSE_OK;
 }
 
@@ -63,6 +65,8 @@ int prep_maxpool(HFUSE_MAXPOOL_PARAMS(), MaxPoolArgs& a) {
     a.mode = (kh == 2 && kw == 2 && sh == 2 && sw == 2 && ph == 0 && pw == 0 && dh == 1 && dw == 1 &&
               (pW % 4) == 0 && (W % 4) == 0 && 2LL * pH <= H && 2LL * pW <= W && items <= kMaxItems)
                  ? 1 : 0;
+    a.div_p4 = make_fastdiv(a.mode == 1 ? (uint32_t)(pW / 4) : 1u);
+    a.div_ph = make_fastdiv((uint32_t)pH);
     return HFUSE_OK;
 }
 
@@ -76,7 +80,7 @@ int prep_bnstats(HFUSE_BNSTATS_PARAMS(), BnStatsArgs& a) {
     a.total = (float)((double)N * (double)HW);
     a.mean = mean; a.invstd = invstd; a.moments = moments;
     a.partial = nullptr; a.tickets = nullptr;
-    a.S = 1; a.chunk = 0; a.per_channel = 0;
+    a.S = 1; a.chunk = 0; a.per_channel = 0; a.per_img = 1; a.div_img = make_fastdiv(1);
     a.vec = (HW % 4) == 0;
     a.ws = workspace; a.ws_bytes = workspace_bytes;
     return HFUSE_OK;
@@ -100,6 +104,8 @@ int prep_upsample(HFUSE_UPSAMPLE_PARAMS(), UpsampleArgs& a) {
     a.mode = ((outW % 4) == 0 && items <= kMaxItems) ? 1 : 0;
     const long long strips = (long long)N * C * (H + 1LL) * (W / 4);
     if (!align_corners && outH == 2LL * H && outW == 2LL * W && (W % 4) == 0 && strips <= kMaxItems) a.mode = 2;
+    a.div_w4 = make_fastdiv(a.mode == 2 ? (uint32_t)(W / 4) : 1u);
+    a.div_j = make_fastdiv((uint32_t)H + 1u);
     return HFUSE_OK;
 }
 

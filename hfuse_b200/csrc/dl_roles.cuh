@@ -29,6 +29,7 @@ struct Im2colArgs {
     int kh, kw, ph, pw, sh, sw, dh, dw;
     int Hc, Wc;
     int mode;   // 0 = generic (one output element per item), 1 = 3x3 stride-1 tile path
+    FastDiv div_w4, div_hc;   // tile path: by Wc/4 and by Hc
 };
 
 struct Im2colRole {
@@ -44,33 +45,48 @@ struct Im2colRole {
     template <int T>
     static __device__ __forceinline__ void run_k3s1(const Args& a, const RoleCtx& ctx) {
         constexpr int KH = 3, KW = 3;
-        const unsigned W4 = (unsigned)a.Wc >> 2;
-        const unsigned Hc = (unsigned)a.Hc;
-        const unsigned total = (unsigned)a.N * a.C * Hc * W4;     // host guarantees < 2^31
+        const unsigned total = (unsigned)a.N * a.C * a.Hc * (a.Wc >> 2);     // host guarantees < 2^31
         const size_t tap_stride = (size_t)a.Hc * a.Wc;
+        // pad 1 and W % 4 == 0: the four centre columns are one aligned 16-byte load and the two
+        // outer columns are the neighbouring lanes' centre values (a warp walks along a row)
         const bool vec_mid = (a.pw == 1) && ((a.W & 3) == 0);
-        for (unsigned it = (unsigned)ctx.block * T + ctx.tid; it < total; it += (unsigned)ctx.nblocks * T) {
-            const unsigned w4 = it % W4;
-            const unsigned r = it / W4;
-            const unsigned h = r % Hc;
-            const unsigned plane = r / Hc;
+        const unsigned lane = ctx.tid & 31;
+        // warp-uniform trip count: every lane takes part in the shuffles
+        for (unsigned base = (unsigned)ctx.block * T + (ctx.tid & ~31); base < total;
+             base += (unsigned)ctx.nblocks * T) {
+            const bool live = base + lane < total;
+            const unsigned it = live ? base + lane : total - 1;
+            unsigned w4, h;
+            const unsigned r = fast_divmod(it, a.div_w4, w4);
+            const unsigned plane = fast_divmod(r, a.div_hc, h);
             const float* src = a.im + (size_t)plane * a.H * a.W;
-            float* dst = a.col + (size_t)plane * (KH * KW) * tap_stride + (size_t)h * a.Wc + w4 * 4;
+            float* dst = a.col + (size_t)plane * (KH * KW) * tap_stride + h * a.Wc + w4 * 4;
             const int wi0 = (int)(w4 * 4) - a.pw;
             float v[KH][4 + KW - 1];
+            if (vec_mid) {
+                // neighbours in the same row sit in lanes +-1 unless the row (or the warp) ends there
+                const bool has_l = w4 > 0, has_r = (int)(w4 * 4) + 4 < a.W;
 #pragma unroll
-            for (int i = 0; i < KH; ++i) {
-                const int hi = (int)h - a.ph + i;
-                const bool row_ok = (hi >= 0) && (hi < a.H);
-                const float* row = src + (size_t)(row_ok ? hi : 0) * a.W;
-                if (vec_mid && (wi0 + 1 + 3 < a.W)) {
-                    // columns wi0+1 .. wi0+4 start on a 16-byte boundary
-                    float4 m = row_ok ? __ldg(reinterpret_cast<const float4*>(row + wi0 + 1))
-                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int i = 0; i < KH; ++i) {
+                    const int hi = (int)h - a.ph + i;
+                    const bool row_ok = (hi >= 0) && (hi < a.H);
+                    const float* row = src + (size_t)(row_ok ? hi : 0) * a.W + w4 * 4;
+                    const float4 m = row_ok ? __ldg(reinterpret_cast<const float4*>(row))
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+                    float left = __shfl_up_sync(0xffffffffu, m.w, 1);
+                    float right = __shfl_down_sync(0xffffffffu, m.x, 1);
+                    if (lane == 0 && has_l) left = row_ok ? __ldg(row - 1) : 0.f;
+                    if (lane == 31 && has_r) right = row_ok ? __ldg(row + 4) : 0.f;
+                    v[i][0] = has_l ? left : 0.f;
                     v[i][1] = m.x; v[i][2] = m.y; v[i][3] = m.z; v[i][4] = m.w;
-                    v[i][0] = (row_ok && wi0 >= 0) ? __ldg(row + wi0) : 0.f;
-                    v[i][5] = (row_ok && wi0 + 5 < a.W) ? __ldg(row + wi0 + 5) : 0.f;
-                } else {
+                    v[i][5] = has_r ? right : 0.f;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < KH; ++i) {
+                    const int hi = (int)h - a.ph + i;
+                    const bool row_ok = (hi >= 0) && (hi < a.H);
+                    const float* row = src + (size_t)(row_ok ? hi : 0) * a.W;
 #pragma unroll
                     for (int x = 0; x < 4 + KW - 1; ++x) {
                         const int wi = wi0 + x;
@@ -78,6 +94,7 @@ struct Im2colRole {
                     }
                 }
             }
+            if (!live) continue;
 #pragma unroll
             for (int i = 0; i < KH; ++i)
 #pragma unroll
@@ -127,6 +144,7 @@ struct MaxPoolArgs {
     int N, C, H, W, pH, pW;
     int kh, kw, sh, sw, ph, pw, dh, dw;
     int mode;   // 0 = generic, 1 = 2x2 stride 2 without padding, pW % 4 == 0, W % 4 == 0
+    FastDiv div_p4, div_ph;   // 2x2 path: by pW/4 and by pH
 };
 
 __device__ __forceinline__ void pool_take(float v, int at, float& best, int& best_at) {
@@ -147,10 +165,9 @@ struct MaxPoolRole {
         const unsigned pH = (unsigned)a.pH;
         const unsigned total = (unsigned)a.N * a.C * pH * P4;      // host guarantees < 2^31
         for (unsigned it = (unsigned)ctx.block * T + ctx.tid; it < total; it += (unsigned)ctx.nblocks * T) {
-            const unsigned p4 = it % P4;
-            const unsigned r = it / P4;
-            const unsigned oh = r % pH;
-            const unsigned plane = r / pH;
+            unsigned p4, oh;
+            const unsigned r = fast_divmod(it, a.div_p4, p4);
+            const unsigned plane = fast_divmod(r, a.div_ph, oh);
             const float* row0 = a.in + (size_t)plane * a.H * a.W + (size_t)(2 * oh) * a.W + 8 * p4;
             const float4 t0 = ldg_stream4(row0), t1 = ldg_stream4(row0 + 4);
             const float4 b0 = ldg_stream4(row0 + a.W), b1 = ldg_stream4(row0 + a.W + 4);
@@ -218,6 +235,7 @@ struct UpsampleArgs {
     int align_corners;
     int mode;   // 0 = one output per item, 1 = four adjacent outputs per item (outW % 4 == 0),
                 // 2 = exact x2 strip path (run_x2)
+    FastDiv div_w4, div_j;   // x2 path: by W/4 and by H+1
 };
 
 __device__ __forceinline__ void bilinear_src(float scale, int dst, int align, int in_size, int& i1, int& i1p,
@@ -289,24 +307,35 @@ struct UpsampleRole {
         const unsigned W4 = (unsigned)a.W >> 2;
         const unsigned J = (unsigned)a.H + 1;                        // row pairs per plane
         const unsigned total = (unsigned)a.N * a.C * J * W4;         // host guarantees < 2^31
-        for (unsigned it = (unsigned)ctx.block * T + ctx.tid; it < total; it += (unsigned)ctx.nblocks * T) {
-            const unsigned m = it % W4;
-            const unsigned r = it / W4;
-            const int j = (int)(r % J);
-            const unsigned plane = r / J;
+        const unsigned lane = ctx.tid & 31;
+        // warp-uniform trip count: every lane takes part in the shuffles
+        for (unsigned base = (unsigned)ctx.block * T + (ctx.tid & ~31); base < total;
+             base += (unsigned)ctx.nblocks * T) {
+            const bool live = base + lane < total;
+            const unsigned it = live ? base + lane : total - 1;
+            unsigned m, ju;
+            const unsigned r = fast_divmod(it, a.div_w4, m);
+            const unsigned plane = fast_divmod(r, a.div_j, ju);
+            const int j = (int)ju;
             // output rows 2j-1 (if j >= 1) and 2j (if j <= H-1) blend input rows ra and rb
             const int ra = j > 0 ? j - 1 : 0;
             const int rb = j == 0 ? (a.H > 1 ? 1 : 0) : (j < a.H ? j : a.H - 1);
-            const float* pa = a.in + (size_t)plane * a.H * a.W + (size_t)ra * a.W + 4 * m;
-            const float* pb = a.in + (size_t)plane * a.H * a.W + (size_t)rb * a.W + 4 * m;
+            const float* pa = a.in + (size_t)plane * a.H * a.W + ra * a.W + 4 * m;
+            const float* pb = a.in + (size_t)plane * a.H * a.W + rb * a.W + 4 * m;
             const bool has_l = m > 0, has_r = m + 1 < W4;
             const float4 qa = __ldg(reinterpret_cast<const float4*>(pa));
             const float4 qb = __ldg(reinterpret_cast<const float4*>(pb));
+            // columns 4m-1 and 4m+4 are the neighbouring lanes' values unless the row (or the warp) ends
+            float la = __shfl_up_sync(0xffffffffu, qa.w, 1), lb = __shfl_up_sync(0xffffffffu, qb.w, 1);
+            float ra_ = __shfl_down_sync(0xffffffffu, qa.x, 1), rb_ = __shfl_down_sync(0xffffffffu, qb.x, 1);
+            if (lane == 0 && has_l) { la = __ldg(pa - 1); lb = __ldg(pb - 1); }
+            if (lane == 31 && has_r) { ra_ = __ldg(pa + 4); rb_ = __ldg(pb + 4); }
+            if (!live) continue;
             float ca[6], cb[6];          // columns 4m-1 .. 4m+4
             ca[1] = qa.x; ca[2] = qa.y; ca[3] = qa.z; ca[4] = qa.w;
             cb[1] = qb.x; cb[2] = qb.y; cb[3] = qb.z; cb[4] = qb.w;
-            ca[0] = has_l ? __ldg(pa - 1) : 0.f;  cb[0] = has_l ? __ldg(pb - 1) : 0.f;
-            ca[5] = has_r ? __ldg(pa + 4) : ca[4]; cb[5] = has_r ? __ldg(pb + 4) : cb[4];   // w1p = 0 at the edge
+            ca[0] = has_l ? la : 0.f;  cb[0] = has_l ? lb : 0.f;
+            ca[5] = has_r ? ra_ : ca[4]; cb[5] = has_r ? rb_ : cb[4];   // w1p = 0 at the edge
             // horizontal blends of both input rows for output columns 8m .. 8m+7
             float ta[8], tb[8];
 #pragma unroll
@@ -401,40 +430,68 @@ struct HistcRole {
         return 0;
     }
 
-    static __device__ __forceinline__ void tally(const Args& a, float v, unsigned* hist) {
-        if (v >= a.lo && v <= a.hi) {
-            const float t = __fmul_rn(__fsub_rn(v, a.lo), (float)a.nbins);
-            const float q = a.range_pow2 ? __fmul_rn(t, a.inv_range) : __fdiv_rn(t, a.range);
-            int b = (int)q;
-            if (b == a.nbins) b -= 1;
-            atomicAdd(hist + b, 1u);
+    static __device__ __forceinline__ void red_shared_inc(uint32_t saddr) {
+        asm volatile("red.shared.add.u32 [%0], 1;" ::"r"(saddr) : "memory");
+    }
+
+    // bin of v, or -1 when v is outside [lo, hi] or NaN
+    static __device__ __forceinline__ int bin_of(const Args& a, float v) {
+        if (!(v >= a.lo && v <= a.hi)) return -1;
+        const float t = __fmul_rn(__fsub_rn(v, a.lo), (float)a.nbins);
+        const float q = a.range_pow2 ? __fmul_rn(t, a.inv_range) : __fdiv_rn(t, a.range);
+        const int b = (int)q;
+        return b == a.nbins ? b - 1 : b;
+    }
+
+    // SHARED selects the address space at compile time: the shared-memory histogram is
+    // updated with `red.shared` (no return value, no generic-address atomics)
+    template <int T, bool SHARED>
+    static __device__ __forceinline__ void sweep(const Args& a, const RoleCtx& ctx, unsigned* hist) {
+        const long long n4 = a.n >> 2;
+        const uint32_t sbase = SHARED ? (uint32_t)__cvta_generic_to_shared(hist) : 0u;
+        for (long long i = (long long)ctx.block * T + ctx.tid; i < n4; i += (long long)ctx.nblocks * T) {
+            const float4 v = ldg_stream4(a.x + 4 * i);
+            const int b0 = bin_of(a, v.x), b1 = bin_of(a, v.y), b2 = bin_of(a, v.z), b3 = bin_of(a, v.w);
+            if (SHARED) {
+                if (b0 >= 0) red_shared_inc(sbase + 4u * b0);
+                if (b1 >= 0) red_shared_inc(sbase + 4u * b1);
+                if (b2 >= 0) red_shared_inc(sbase + 4u * b2);
+                if (b3 >= 0) red_shared_inc(sbase + 4u * b3);
+            } else {
+                if (b0 >= 0) atomicAdd(hist + b0, 1u);
+                if (b1 >= 0) atomicAdd(hist + b1, 1u);
+                if (b2 >= 0) atomicAdd(hist + b2, 1u);
+                if (b3 >= 0) atomicAdd(hist + b3, 1u);
+            }
+        }
+        if (ctx.block == 0) {   // ragged tail (n % 4 values)
+            for (long long i = 4 * n4 + ctx.tid; i < a.n; i += T) {
+                const int b = bin_of(a, __ldg(a.x + i));
+                if (b >= 0) {
+                    if (SHARED) red_shared_inc(sbase + 4u * b);
+                    else atomicAdd(hist + b, 1u);
+                }
+            }
         }
     }
 
     template <int T, int BAR>
     static __device__ __forceinline__ void run(const Args& a, const RoleCtx& ctx) {
+        if (a.copies == 0) {
+            sweep<T, false>(a, ctx, a.counts);
+            return;
+        }
         unsigned* sh = reinterpret_cast<unsigned*>(ctx.smem);
-        unsigned* hist = a.counts;
-        if (a.copies > 0) {
-            for (int i = ctx.tid; i < a.copies * a.nbins; i += T) sh[i] = 0u;
-            role_sync<BAR, T>();
-            hist = sh + ((ctx.tid >> 5) % a.copies) * a.nbins;
-        }
-        const long long n4 = a.n >> 2;
-        for (long long i = (long long)ctx.block * T + ctx.tid; i < n4; i += (long long)ctx.nblocks * T) {
-            const float4 v = ldg_stream4(a.x + 4 * i);
-            tally(a, v.x, hist); tally(a, v.y, hist); tally(a, v.z, hist); tally(a, v.w, hist);
-        }
-        if (ctx.block == 0) {   // ragged tail (n % 4 values)
-            for (long long i = 4 * n4 + ctx.tid; i < a.n; i += T) tally(a, __ldg(a.x + i), hist);
-        }
-        if (a.copies > 0) {
-            role_sync<BAR, T>();
-            for (int b = ctx.tid; b < a.nbins; b += T) {
-                unsigned s = 0;
-                for (int c = 0; c < a.copies; ++c) s += sh[c * a.nbins + b];
-                if (s) atomicAdd(a.counts + b, s);
-            }
+        for (int i = ctx.tid; i < a.copies * a.nbins; i += T) sh[i] = 0u;
+        role_sync<BAR, T>();
+        // the shared window address keeps the accesses in the shared state space
+        unsigned* hist = sh + ((ctx.tid >> 5) % a.copies) * a.nbins;
+        sweep<T, true>(a, ctx, hist);
+        role_sync<BAR, T>();
+        for (int b = ctx.tid; b < a.nbins; b += T) {
+            unsigned s = 0;
+            for (int c = 0; c < a.copies; ++c) s += sh[c * a.nbins + b];
+            if (s) atomicAdd(a.counts + b, s);
         }
     }
 };
@@ -443,13 +500,15 @@ struct HistcRole {
 // batch_norm_collect_statistics: per-channel mean and 1/sqrt(biased var + eps)
 // =============================================================================
 // Work unit = (channel, slice): the channel's N*HW values, taken in (n, hw)
-// order, are cut into S equal slices and ONE WARP reduces one slice: each lane
-// accumulates shifted sums over its 16-byte loads, converts them to Welford
-// moments (count, mean, M2) and the warp folds them with a shuffle tree of
-// Chan merges.  With S > 1 the slice moments go to scratch and the warp that
-// takes the last ticket of a channel folds all S of them in slice order, so
-// the result does not depend on arrival order.  A warp never waits for
-// another one, so the role needs no barrier and no shared memory.
+// order, are cut into S equal slices and the whole role (T threads) reduces
+// one slice: each thread accumulates shifted sums over its 16-byte loads and
+// turns them into Welford moments (count, mean, M2); a warp folds them with a
+// shuffle tree of Chan merges; the per-warp moments meet in shared memory
+// behind the role's named barrier and warp 0 folds them.  S = 1 (a whole
+// channel per unit) whenever there are at least about as many channels as
+// blocks; otherwise the slice moments go to scratch and the block that takes
+// the last ticket of a channel folds all S of them in slice order, so the
+// result does not depend on arrival order.
 struct BnStatsArgs {
     const float* x;       // [N][C][HW]
     int N, C, HW;
@@ -463,6 +522,8 @@ struct BnStatsArgs {
     int S;                // slices per channel (<= kBnMaxSlices)
     unsigned chunk;       // vector (or scalar) items per slice
     unsigned per_channel; // vector (or scalar) items per channel = N * HW / (vec ? 4 : 1)
+    unsigned per_img;     // vector (or scalar) items per image
+    FastDiv div_img;      // by per_img
     int vec;              // HW % 4 == 0: 16-byte loads
     size_t ws_bytes;      // size of the caller's scratch buffer (host-side check only)
     void* ws;             // the caller's scratch buffer
@@ -504,20 +565,21 @@ __device__ __forceinline__ Moments warp_merge(Moments m) {
 
 struct BnStatsRole {
     using Args = BnStatsArgs;
-    static int smem_bytes(const Args&, int) { return 0; }
+    // two parity buffers of per-warp moments
+    static int smem_bytes(const Args&, int T) { return 2 * 3 * (T / 32) * (int)sizeof(float); }
 
-    // Slices per channel: about two units per resident warp, but never less
-    // than two loads per lane in a slice.
+    // One channel per unit when the channels alone give every block work;
+    // otherwise S slices per channel, but never fewer than two loads per thread in a slice.
     static int plan(Args& a, int T, int grid) {
         const long long per_channel = (long long)a.N * a.HW / (a.vec ? 4 : 1);
-        long long s_small = per_channel / 64;
+        long long s_small = per_channel / (2LL * T);
         if (s_small < 1) s_small = 1;
         if (s_small > kBnMaxSlices) s_small = kBnMaxSlices;
-        const long long warps = (long long)grid * (T / 32);
-        long long s_want = (2 * warps + a.C - 1) / a.C;
-        if (s_want < 1) s_want = 1;
+        long long s_want = (2LL * a.C >= grid) ? 1 : (grid + a.C - 1) / a.C;
         const long long S = s_want < s_small ? s_want : s_small;
         a.per_channel = (unsigned)per_channel;
+        a.per_img = (unsigned)(a.vec ? a.HW / 4 : a.HW);
+        a.div_img = make_fastdiv(a.per_img);
         a.chunk = (unsigned)((per_channel + S - 1) / S);
         a.S = (int)((per_channel + a.chunk - 1) / a.chunk);
         if (a.S > 1) {
@@ -544,26 +606,31 @@ struct BnStatsRole {
     static __device__ __forceinline__ void run(const Args& a, const RoleCtx& ctx) {
         constexpr int NW = T / 32;
         constexpr int UNROLL = 4;
-        const int lane = ctx.tid & 31;
+        static_assert(NW <= 32, "one warp folds the per-warp moments");
+        float* sh = reinterpret_cast<float*>(ctx.smem);
+        const int lane = ctx.tid & 31, warp = ctx.tid >> 5;
         const unsigned units = (unsigned)a.C * (unsigned)a.S;
-        const unsigned per_img = a.vec ? (unsigned)a.HW >> 2 : (unsigned)a.HW;
-        for (unsigned u = (unsigned)ctx.block * NW + (ctx.tid >> 5); u < units; u += (unsigned)ctx.nblocks * NW) {
+        int parity = 0;
+        for (unsigned u = ctx.block; u < units; u += ctx.nblocks, parity ^= 1) {
             const unsigned c = u / a.S, s = u - c * a.S;
             const unsigned k0 = s * a.chunk;
             const unsigned k1 = min(k0 + a.chunk, a.per_channel);
-            // ---- per-lane sums of (x - shift) and (x - shift)^2; shift = the lane's first value
+            const float* xc = a.x + (size_t)c * a.HW;
+            const size_t img_stride = (size_t)a.C * a.HW;
+            // ---- per-thread sums of (x - shift) and (x - shift)^2; shift = the thread's first value
             float cnt = 0.f, sum = 0.f, sq = 0.f, shift = 0.f;
-            for (unsigned k = k0 + lane; k < k1; k += 32 * UNROLL) {
+            for (unsigned k = k0 + ctx.tid; k < k1; k += T * UNROLL) {
                 if (a.vec) {
                     float4 v[UNROLL];
                     bool ok[UNROLL];
 #pragma unroll
                     for (int j = 0; j < UNROLL; ++j) {
-                        const unsigned kk = k + 32 * j;
+                        const unsigned kk = k + T * j;
                         ok[j] = kk < k1;
                         if (ok[j]) {
-                            const unsigned n = kk / per_img, off = kk - n * per_img;
-                            v[j] = ldg_stream4(a.x + ((size_t)n * a.C + c) * a.HW + 4 * off);
+                            unsigned off;
+                            const unsigned n = fast_divmod(kk, a.div_img, off);
+                            v[j] = ldg_stream4(xc + n * img_stride + 4 * off);
                         }
                     }
 #pragma unroll
@@ -580,11 +647,12 @@ struct BnStatsRole {
                     bool ok[UNROLL];
 #pragma unroll
                     for (int j = 0; j < UNROLL; ++j) {
-                        const unsigned kk = k + 32 * j;
+                        const unsigned kk = k + T * j;
                         ok[j] = kk < k1;
                         if (ok[j]) {
-                            const unsigned n = kk / per_img, off = kk - n * per_img;
-                            v[j] = __ldg(a.x + ((size_t)n * a.C + c) * a.HW + off);
+                            unsigned off;
+                            const unsigned n = fast_divmod(kk, a.div_img, off);
+                            v[j] = __ldg(xc + n * img_stride + off);
                         }
                     }
 #pragma unroll
@@ -603,16 +671,25 @@ struct BnStatsRole {
                 const float dm = sum / cnt;
                 m = Moments{cnt, shift + dm, fmaxf(sq - sum * dm, 0.f)};
             }
+            // ---- warp fold, then the role-wide fold through shared memory and the role's barrier
             m = warp_merge(m);
+            float* buf = sh + parity * 3 * NW;
+            if (lane == 0) { buf[warp] = m.n; buf[NW + warp] = m.mean; buf[2 * NW + warp] = m.m2; }
+            role_sync<BAR, T>();
+            // The parity buffer keeps warp 0's reads of this unit apart from the next unit's
+            // writes; the unit after that is fenced by the next barrier.
+            if (warp != 0) continue;
+            Moments w = (lane < NW) ? Moments{buf[lane], buf[NW + lane], buf[2 * NW + lane]} : Moments{0.f, 0.f, 0.f};
+            w = warp_merge(w);
             if (a.S == 1) {
-                if (lane == 0) finish(a, (int)c, m);
+                if (lane == 0) finish(a, (int)c, w);
                 continue;
             }
-            // publish this slice; the warp that takes the last ticket folds all slices
+            // publish this slice; the block that takes the last ticket folds all slices
             unsigned ticket = 0;
             if (lane == 0) {
                 float* p = a.partial + ((size_t)c * a.S + s) * 3;
-                __stcg(p, m.n); __stcg(p + 1, m.mean); __stcg(p + 2, m.m2);
+                __stcg(p, w.n); __stcg(p + 1, w.mean); __stcg(p + 2, w.m2);
                 __threadfence();
                 ticket = atomicAdd(a.tickets + c, 1u);
             }
