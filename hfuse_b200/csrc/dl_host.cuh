@@ -121,6 +121,7 @@ int prep_histc(HFUSE_HISTC_PARAMS(), HistcArgs& a) {
     a.range_pow2 = (mant == 0.5f) && (e > -100) && (e < 100);
     a.inv_range = a.range_pow2 ? 1.f / a.range : 0.f;
     a.copies = 0;
+    a.lane_private = 0;
     return HFUSE_OK;
 }
 

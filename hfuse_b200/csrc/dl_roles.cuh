@@ -415,14 +415,26 @@ struct HistcArgs {
     int range_pow2;     // range is a power of two: multiplying by inv_range equals dividing by range
     unsigned* counts;   // zeroed by the caller (the entry point clears it on the stream)
     int copies;         // private shared-memory histograms per role (0 = global atomics only)
+    int lane_private;   // shared histogram laid out [bin][32 lanes]: lane l only ever touches bank l
 };
 
 struct HistcRole {
     using Args = HistcArgs;
-    static int smem_bytes(const Args& a, int) { return a.copies * a.nbins * (int)sizeof(unsigned); }
-    // one private histogram per warp while that fits in 16 KB of shared memory,
-    // fewer (shared between warps) beyond that, none when a single copy would not fit
+    static int smem_bytes(const Args& a, int) {
+        return (a.lane_private ? 32 : a.copies) * a.nbins * (int)sizeof(unsigned);
+    }
+    // Up to 256 bins: one counter per (bin, lane) = 32 KB at most.  Lane l of every warp
+    // only touches word bin*32 + l, i.e. bank l, so a warp's 32 increments never meet in a
+    // bank or an address whatever the data looks like.  Beyond that: one private histogram
+    // per warp while that fits in 16 KB, fewer (shared between warps) for more bins, global
+    // atomics only when a single copy would not fit.
     static int plan(Args& a, int T, int) {
+        if (a.nbins <= 256) {
+            a.lane_private = 1;
+            a.copies = 1;
+            return 0;
+        }
+        a.lane_private = 0;
         const int budget = 16 * 1024;
         int copies = budget / (a.nbins * (int)sizeof(unsigned));
         if (copies > T / 32) copies = T / 32;
@@ -448,15 +460,18 @@ struct HistcRole {
     template <int T, bool SHARED>
     static __device__ __forceinline__ void sweep(const Args& a, const RoleCtx& ctx, unsigned* hist) {
         const long long n4 = a.n >> 2;
-        const uint32_t sbase = SHARED ? (uint32_t)__cvta_generic_to_shared(hist) : 0u;
+        // shared address of bin b is sbase + 4 * (b << shift): shift = 5 spreads a bin over 32 lanes
+        const int shift = (SHARED && a.lane_private) ? 5 : 0;
+        const uint32_t sbase = SHARED ? (uint32_t)__cvta_generic_to_shared(hist) + (a.lane_private ? 4u * (ctx.tid & 31) : 0u)
+                                      : 0u;
         for (long long i = (long long)ctx.block * T + ctx.tid; i < n4; i += (long long)ctx.nblocks * T) {
             const float4 v = ldg_stream4(a.x + 4 * i);
             const int b0 = bin_of(a, v.x), b1 = bin_of(a, v.y), b2 = bin_of(a, v.z), b3 = bin_of(a, v.w);
             if (SHARED) {
-                if (b0 >= 0) red_shared_inc(sbase + 4u * b0);
-                if (b1 >= 0) red_shared_inc(sbase + 4u * b1);
-                if (b2 >= 0) red_shared_inc(sbase + 4u * b2);
-                if (b3 >= 0) red_shared_inc(sbase + 4u * b3);
+                if (b0 >= 0) red_shared_inc(sbase + (4u * b0 << shift));
+                if (b1 >= 0) red_shared_inc(sbase + (4u * b1 << shift));
+                if (b2 >= 0) red_shared_inc(sbase + (4u * b2 << shift));
+                if (b3 >= 0) red_shared_inc(sbase + (4u * b3 << shift));
             } else {
                 if (b0 >= 0) atomicAdd(hist + b0, 1u);
                 if (b1 >= 0) atomicAdd(hist + b1, 1u);
@@ -468,7 +483,7 @@ struct HistcRole {
             for (long long i = 4 * n4 + ctx.tid; i < a.n; i += T) {
                 const int b = bin_of(a, __ldg(a.x + i));
                 if (b >= 0) {
-                    if (SHARED) red_shared_inc(sbase + 4u * b);
+                    if (SHARED) red_shared_inc(sbase + (4u * b << shift));
                     else atomicAdd(hist + b, 1u);
                 }
             }
@@ -482,15 +497,20 @@ struct HistcRole {
             return;
         }
         unsigned* sh = reinterpret_cast<unsigned*>(ctx.smem);
-        for (int i = ctx.tid; i < a.copies * a.nbins; i += T) sh[i] = 0u;
+        const int words = (a.lane_private ? 32 : a.copies) * a.nbins;
+        for (int i = ctx.tid; i < words; i += T) sh[i] = 0u;
         role_sync<BAR, T>();
-        // the shared window address keeps the accesses in the shared state space
-        unsigned* hist = sh + ((ctx.tid >> 5) % a.copies) * a.nbins;
+        unsigned* hist = a.lane_private ? sh : sh + ((ctx.tid >> 5) % a.copies) * a.nbins;
         sweep<T, true>(a, ctx, hist);
         role_sync<BAR, T>();
         for (int b = ctx.tid; b < a.nbins; b += T) {
             unsigned s = 0;
-            for (int c = 0; c < a.copies; ++c) s += sh[c * a.nbins + b];
+            if (a.lane_private) {
+                // rotate the start so that the threads of a warp read different banks
+                for (int l = 0; l < 32; ++l) s += sh[b * 32 + ((l + ctx.tid) & 31)];
+            } else {
+                for (int c = 0; c < a.copies; ++c) s += sh[c * a.nbins + b];
+            }
             if (s) atomicAdd(a.counts + b, s);
         }
     }
