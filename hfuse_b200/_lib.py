@@ -12,6 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libhfuse_b200.so")
 
 HFUSE_MAX_HITS = 256
+HFUSE_NOALLOC_MAX_CHANNELS = 1024
 
 _p, _i, _f = C.c_void_p, C.c_int, C.c_float
 _i64, _u64, _u32, _sz = C.c_int64, C.c_uint64, C.c_uint32, C.c_size_t
@@ -59,7 +60,7 @@ def exported_symbols() -> list[str]:
     """Every function include/hfuse_b200.h declares."""
     names = list(DL_SOLO.values()) + [f"hfuse_{p}_f32" for p in DL_PAIRS]
     names += list(CRYPTO_SOLO.values()) + [f"hfuse_{p}_search" for p in CRYPTO_PAIRS]
-    names += ["hfuse_error_string", "hfuse_version", "hfuse_bnstats_workspace_bytes",
+    names += ["hfuse_error_string", "hfuse_version", "hfuse_bnstats_workspace_bytes", "hfuse_bnstats_noalloc_f32",
               "hfuse_bnstats_finalize_f64", "hfuse_hits_reset", "hfuse_hash_batch", "hfuse_tune_set",
               "hfuse_tune_describe", "hfuse_xoshiro256ss_fill"]
     return names
@@ -100,6 +101,8 @@ def lib() -> C.CDLL:
     L.hfuse_bnstats_workspace_bytes.restype, L.hfuse_bnstats_workspace_bytes.argtypes = _sz, [_i, _i, _i]
     L.hfuse_bnstats_finalize_f64.restype = _i
     L.hfuse_bnstats_finalize_f64.argtypes = [_p, _i, _f, _p, _p, _p]
+    L.hfuse_bnstats_noalloc_f32.restype = _i
+    L.hfuse_bnstats_noalloc_f32.argtypes = [_p, _i, _i, _i, _f, _p, _p, _p, _p]
     L.hfuse_hits_reset.restype, L.hfuse_hits_reset.argtypes = _i, [_p, _p]
     L.hfuse_hash_batch.restype = _i
     L.hfuse_hash_batch.argtypes = [_i, C.c_char_p, _p, _u32, _u64, _u32, _p, _p, _p]

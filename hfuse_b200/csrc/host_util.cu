@@ -19,6 +19,8 @@ const char* hfuse_error_string(int code) {
     case HFUSE_ERR_LAUNCH: return "CUDA reported an error at launch";
     case HFUSE_ERR_NO_DEVICE: return "no usable sm_100 device";
     case HFUSE_ERR_UNKNOWN_PAIR: return "unknown kernel or pair name";
+    case HFUSE_ERR_NOALLOC_LIMIT:
+        return "more channels than the built-in scratch of the no-allocation entry point serves (HFUSE_NOALLOC_MAX_CHANNELS)";
     }
     return "unknown error code";
 }

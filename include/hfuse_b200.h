@@ -45,7 +45,8 @@ enum {
     HFUSE_ERR_WORKSPACE = -4,   /* scratch buffer missing or too small */
     HFUSE_ERR_LAUNCH = -5,      /* cudaGetLastError() after the launch was not cudaSuccess */
     HFUSE_ERR_NO_DEVICE = -6,   /* no usable sm_100 device */
-    HFUSE_ERR_UNKNOWN_PAIR = -7
+    HFUSE_ERR_UNKNOWN_PAIR = -7,
+    HFUSE_ERR_NOALLOC_LIMIT = -8 /* more channels than the built-in scratch of the no-allocation entry serves */
 };
 
 HFUSE_API const char* hfuse_error_string(int code);
@@ -114,6 +115,21 @@ HFUSE_API size_t hfuse_bnstats_workspace_bytes(int N, int C, int HW);
  * which is single-GPU): mean = s1/n, var = s2/n - mean^2, invstd = 1/sqrt(var + eps). */
 HFUSE_API int hfuse_bnstats_finalize_f64(const double* moments, int C, float eps, float* mean,
                                          float* invstd, hfuse_stream_t stream);
+
+/* Batch-norm statistics without any caller-provided scratch.  It has no counterpart in the
+ * reference; it exists for callers that cannot allocate device memory at the point of the
+ * call (inside a framework's memory-planning phase, behind a plugin interface that passes
+ * inputs and outputs only, or on a thread that must stay out of the allocator).  Same
+ * arguments and results as hfuse_bnstats_f32 minus the workspace; the scratch is a static
+ * device array inside the library (3,149,824 bytes on every GPU that loads it, held until
+ * exit), which limits C to HFUSE_NOALLOC_MAX_CHANNELS (larger C returns
+ * HFUSE_ERR_NOALLOC_LIMIT).  The call itself allocates nothing.  The first call on each
+ * device looks up the array's address; make that call before any stream capture begins.
+ * All calls on a device share the one array: calls that may overlap on the GPU (different
+ * streams without ordering between them) race and must be serialised by the caller. */
+#define HFUSE_NOALLOC_MAX_CHANNELS 1024
+HFUSE_API int hfuse_bnstats_noalloc_f32(const float* x, int N, int C, int HW, float eps, float* mean,
+                                        float* invstd, double* moments, hfuse_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
  * Fused pairs.  One kernel launch; the block is split into K1's and K2's thread ranges,
