@@ -31,7 +31,8 @@ __device__ __forceinline__ void role_sync() {
 // allocation and stores are marked evict-first.
 __device__ __forceinline__ float4 ldg_stream4(const float* p) {
     float4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+    // not volatile: the data is read-only for the kernel, so the compiler may hoist and batch these loads
+    asm("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
                  : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
     return v;
 }

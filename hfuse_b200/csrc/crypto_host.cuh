@@ -143,7 +143,7 @@ int dispatch_pair(const char* name, int default_variant, typename RA::Args a, ty
     const Tune t = tune_get(name);
     switch (t.variant >= 0 ? t.variant : default_variant) {
 #define X(I, TA, TB, MB) \
-    case I: return launch_pair<RA, RB, TA, TB, MB>(a, b, t.blocks_per_sm, s);
+    case I: return launch_pair_queue<RA, RB, TA, TB, MB>(a, b, t.blocks_per_sm, s);
         CRYPTO_PAIR_VARIANTS(X)
 #undef X
     }

@@ -409,49 +409,74 @@ struct EthashRole {
 };
 
 // ---------------------------------------------------------------------------
-// The sweep every hash shares: a grid-stride loop over the nonce range with a
-// trip count that is uniform per block (ethash lanes must stay together).
+// The sweep every hash shares.
+//   run()   : grid-stride loop over the nonce range (standalone kernels); the trip count is
+//             uniform per block because ethash lanes must stay together.
+//   drain() : work-queue form used by the fused pairs.  Warps take chunks of nonces from a
+//             cursor kept in hfuse_hits::reserved (zeroed by hfuse_hits_reset) until the range is
+//             used up.  A thread range first drains its own hash's queue and then the other
+//             one's, so both ranges finish together whatever the cost ratio of the two hashes.
 // ---------------------------------------------------------------------------
+template <class H> struct NonceIs32 { static constexpr bool value = false; };
+template <> struct NonceIs32<Sha256dRole> { static constexpr bool value = true; };
+template <> struct NonceIs32<Blake256Role> { static constexpr bool value = true; };
+
 template <class Hash>
 struct SearchRole {
     using Args = typename Hash::Args;
     static int smem_bytes(const Args&, int) { return 0; }
     static int plan(Args&, int, int) { return 0; }
 
-    template <int T, int BAR>
-    static __device__ __forceinline__ void run(const Args& a, const RoleCtx& ctx) {
+    // nonce number i of the sweep; every lane of a warp must call this together (ethash)
+    static __device__ __forceinline__ void one(const Args& a, unsigned long long i, bool live) {
         const SearchCommon& c = a.c;
-        const unsigned long long stride = (unsigned long long)ctx.nblocks * T;
-        for (unsigned long long base = (unsigned long long)ctx.block * T; base < c.count; base += stride) {
-            const unsigned long long i = base + ctx.tid;
-            const bool live = i < c.count;
-            unsigned long long nonce = c.start + (live ? i : 0);
-            uint32_t d[8], mix[8];
-            if constexpr (Hash::kCooperative) {
-                Hash::hash(a, nonce, d, mix);
-            } else {
-                if (!live) continue;
-                if constexpr (sizeof(decltype(nonce)) == 8 && !Hash32<Hash>::value) Hash::hash(a, nonce, d);
-                else { nonce = (uint32_t)nonce; Hash::hash(a, (uint32_t)nonce, d); }
-            }
-            if (!live) continue;
-            if (c.out32) {
-                write_digest_be(c.out32, i, d);
-                if (Hash::kCooperative && c.mix32) {
-                    uint32_t* p = reinterpret_cast<uint32_t*>(c.mix32 + 32 * i);
+        unsigned long long nonce = c.start + (live ? i : 0);
+        uint32_t d[8], mix[8];
+        if constexpr (Hash::kCooperative) {
+            Hash::hash(a, nonce, d, mix);
+        } else {
+            if (!live) return;
+            if constexpr (NonceIs32<Hash>::value) { nonce = (uint32_t)nonce; Hash::hash(a, (uint32_t)nonce, d); }
+            else Hash::hash(a, nonce, d);
+        }
+        if (!live) return;
+        if (c.out32) {
+            write_digest_be(c.out32, i, d);
+            if (Hash::kCooperative && c.mix32) {
+                uint32_t* p = reinterpret_cast<uint32_t*>(c.mix32 + 32 * i);
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) p[k] = mix[k];
-                }
-            } else if (d[0] <= c.target[0] && below_target(d, c.target)) {
-                record_hit(c.hits, nonce, Hash::kCooperative ? mix : nullptr);
+                for (int k = 0; k < 8; ++k) p[k] = mix[k];
             }
+        } else if (d[0] <= c.target[0] && below_target(d, c.target)) {
+            record_hit(c.hits, nonce, Hash::kCooperative ? mix : nullptr);
         }
     }
 
-    template <class H> struct Hash32 { static constexpr bool value = false; };
-};
+    template <int T, int BAR>
+    static __device__ __forceinline__ void run(const Args& a, const RoleCtx& ctx) {
+        const unsigned long long stride = (unsigned long long)ctx.nblocks * T;
+        for (unsigned long long base = (unsigned long long)ctx.block * T; base < a.c.count; base += stride) {
+            const unsigned long long i = base + ctx.tid;
+            one(a, i, i < a.c.count);
+        }
+    }
 
-template <> template <> struct SearchRole<Sha256dRole>::Hash32<Sha256dRole> { static constexpr bool value = true; };
-template <> template <> struct SearchRole<Blake256Role>::Hash32<Blake256Role> { static constexpr bool value = true; };
+    static __device__ __forceinline__ void drain(const Args& a, unsigned chunk) {
+        const unsigned lane = threadIdx.x & 31;
+        const unsigned long long nchunks = (a.c.count + chunk - 1) / chunk;
+        for (;;) {
+            unsigned ci = 0;
+            if (lane == 0) ci = atomicAdd(&a.c.hits->reserved, 1u);
+            ci = __shfl_sync(0xffffffffu, ci, 0);
+            if (ci >= nchunks) break;          // every warp overshoots the cursor once, then stops
+            const unsigned long long lo = (unsigned long long)ci * chunk;
+            const unsigned long long hi = lo + chunk < a.c.count ? lo + chunk : a.c.count;
+            for (unsigned long long base = lo; base < hi; base += 32) {
+                const unsigned long long i = base + lane;
+                one(a, i, i < hi);
+            }
+        }
+    }
+};
 
 }  // namespace hfuse

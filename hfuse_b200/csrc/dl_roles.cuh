@@ -464,19 +464,32 @@ struct HistcRole {
         const int shift = (SHARED && a.lane_private) ? 5 : 0;
         const uint32_t sbase = SHARED ? (uint32_t)__cvta_generic_to_shared(hist) + (a.lane_private ? 4u * (ctx.tid & 31) : 0u)
                                       : 0u;
-        for (long long i = (long long)ctx.block * T + ctx.tid; i < n4; i += (long long)ctx.nblocks * T) {
-            const float4 v = ldg_stream4(a.x + 4 * i);
-            const int b0 = bin_of(a, v.x), b1 = bin_of(a, v.y), b2 = bin_of(a, v.z), b3 = bin_of(a, v.w);
-            if (SHARED) {
-                if (b0 >= 0) red_shared_inc(sbase + (4u * b0 << shift));
-                if (b1 >= 0) red_shared_inc(sbase + (4u * b1 << shift));
-                if (b2 >= 0) red_shared_inc(sbase + (4u * b2 << shift));
-                if (b3 >= 0) red_shared_inc(sbase + (4u * b3 << shift));
-            } else {
-                if (b0 >= 0) atomicAdd(hist + b0, 1u);
-                if (b1 >= 0) atomicAdd(hist + b1, 1u);
-                if (b2 >= 0) atomicAdd(hist + b2, 1u);
-                if (b3 >= 0) atomicAdd(hist + b3, 1u);
+        // four 16-byte loads in flight per thread before any of them is binned
+        constexpr int U = 4;
+        const long long stride = (long long)ctx.nblocks * T;
+        for (long long i = (long long)ctx.block * T + ctx.tid; i < n4; i += U * stride) {
+            float4 v[U];
+            bool ok[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                ok[u] = i + u * stride < n4;
+                if (ok[u]) v[u] = ldg_stream4(a.x + 4 * (i + u * stride));
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (!ok[u]) continue;
+                const int b0 = bin_of(a, v[u].x), b1 = bin_of(a, v[u].y), b2 = bin_of(a, v[u].z), b3 = bin_of(a, v[u].w);
+                if (SHARED) {
+                    if (b0 >= 0) red_shared_inc(sbase + (4u * b0 << shift));
+                    if (b1 >= 0) red_shared_inc(sbase + (4u * b1 << shift));
+                    if (b2 >= 0) red_shared_inc(sbase + (4u * b2 << shift));
+                    if (b3 >= 0) red_shared_inc(sbase + (4u * b3 << shift));
+                } else {
+                    if (b0 >= 0) atomicAdd(hist + b0, 1u);
+                    if (b1 >= 0) atomicAdd(hist + b1, 1u);
+                    if (b2 >= 0) atomicAdd(hist + b2, 1u);
+                    if (b3 >= 0) atomicAdd(hist + b3, 1u);
+                }
             }
         }
         if (ctx.block == 0) {   // ragged tail (n % 4 values)

@@ -37,4 +37,20 @@ fused_kernel(const __grid_constant__ typename RoleA::Args a, const __grid_consta
     }
 }
 
+// Fused pair of two work-queue roles (the nonce searches).  The block is still split into
+// role A's and role B's thread ranges; each range drains its own queue first and then helps
+// with the other one, so no range idles while the other still has nonces left.
+template <class RoleA, class RoleB, int TA, int TB, int MINB>
+__global__ void __launch_bounds__(TA + TB, MINB)
+fused_queue_kernel(const __grid_constant__ typename RoleA::Args a, const __grid_constant__ typename RoleB::Args b,
+                   unsigned chunk_a, unsigned chunk_b) {
+    static_assert(TA % 32 == 0 && TB % 32 == 0, "ranges are whole warps, so the guard never splits a warp");
+    int which = ((int)threadIdx.x < TA) ? 0 : 1;
+#pragma unroll 1
+    for (int phase = 0; phase < 2; ++phase, which ^= 1) {
+        if (which == 0) RoleA::drain(a, chunk_a);
+        else RoleB::drain(b, chunk_b);
+    }
+}
+
 }  // namespace hfuse

@@ -112,4 +112,27 @@ int launch_pair(typename RA::Args a, typename RB::Args b, int blocks_per_sm, cud
     return check_launch();
 }
 
+// chunk of nonces a warp takes from a queue at a time: about 16 chunks per resident warp,
+// a multiple of 32, at least 128, and large enough that the 32-bit cursor cannot wrap
+inline unsigned queue_chunk(unsigned long long count, long long warps) {
+    unsigned long long c = count / (unsigned long long)(warps * 16 > 0 ? warps * 16 : 1);
+    if (c > 8192) c = 8192;
+    if (c < 128) c = 128;
+    const unsigned long long floor_c = (count >> 30) + 1;
+    if (c < floor_c) c = floor_c;
+    return (unsigned)((c + 31) / 32 * 32);
+}
+
+template <class RA, class RB, int TA, int TB, int MINB>
+int launch_pair_queue(typename RA::Args a, typename RB::Args b, int blocks_per_sm, cudaStream_t s) {
+    DeviceFacts f;
+    if (int rc = device_facts(f)) return rc;
+    auto kern = fused_queue_kernel<RA, RB, TA, TB, MINB>;
+    const int bps = blocks_per_sm > 0 ? blocks_per_sm : resident_blocks((const void*)kern, TA + TB, 0);
+    const int grid = f.sms * bps;
+    const long long warps = (long long)grid * ((TA + TB) / 32);
+    kern<<<grid, TA + TB, 0, s>>>(a, b, queue_chunk(a.c.count, warps), queue_chunk(b.c.count, warps));
+    return check_launch();
+}
+
 }  // namespace hfuse

@@ -182,9 +182,11 @@ HFUSE_API int hfuse_histc_bnstats_f32(HFUSE_HISTC_PARAMS(a_), HFUSE_BNSTATS_PARA
 #define HFUSE_MAX_HITS 256
 
 /* The result record (replaces the reference's `Search_results`, whose layout is in the
- * absent ethminer sources).  Device memory; `count` must be zero before a search
- * (hfuse_hits_reset) and counts every hit found even beyond HFUSE_MAX_HITS; slots are
- * filled in arrival order, so sort by nonce before comparing. */
+ * absent ethminer sources).  Device memory; reset it before every search (hfuse_hits_reset):
+ * `count` must start at zero and counts every hit found even beyond HFUSE_MAX_HITS; slots
+ * are filled in arrival order, so sort by nonce before comparing.  `reserved` is the work
+ * queue cursor of the fused searches (thread ranges take chunks of nonces from it) and
+ * must also start at zero. */
 typedef struct hfuse_hits {
     uint32_t count;
     uint32_t reserved;
