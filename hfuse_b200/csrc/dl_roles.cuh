@@ -464,17 +464,28 @@ struct HistcRole {
         const int shift = (SHARED && a.lane_private) ? 5 : 0;
         const uint32_t sbase = SHARED ? (uint32_t)__cvta_generic_to_shared(hist) + (a.lane_private ? 4u * (ctx.tid & 31) : 0u)
                                       : 0u;
-        // four 16-byte loads in flight per thread before any of them is binned
+        // Software pipeline: the 16-byte loads of the next iteration are issued before the
+        // current values are binned, so every warp keeps loads in flight while its shared
+        // reductions drain (the reductions cost about four cycles per warp instruction).
         constexpr int U = 4;
         const long long stride = (long long)ctx.nblocks * T;
-        for (long long i = (long long)ctx.block * T + ctx.tid; i < n4; i += U * stride) {
+        long long i = (long long)ctx.block * T + ctx.tid;
+        float4 nxt[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (i + u * stride < n4) nxt[u] = ldg_stream4(a.x + 4 * (i + u * stride));
+        for (; i < n4; i += U * stride) {
             float4 v[U];
             bool ok[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 ok[u] = i + u * stride < n4;
-                if (ok[u]) v[u] = ldg_stream4(a.x + 4 * (i + u * stride));
+                v[u] = nxt[u];
             }
+            const long long j = i + U * stride;
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (j + u * stride < n4) nxt[u] = ldg_stream4(a.x + 4 * (j + u * stride));
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 if (!ok[u]) continue;
