@@ -290,13 +290,27 @@ def run_ours(args):
     NSETS = 6
     name, sets, nbytes = build_dl_sets(torch, ops, workloads, 1, dev, NSETS)
     launches = 0
-    if use_dist:
-        # per-GPU moments -> all-reduce on a side stream (overlaps the next step) -> finalize
+    done = [None] * NSETS
+    collective = "none"
+    if use_dist and args.collective == "fused":
+        # the cross-GPU sum of the moments happens inside the fused kernel, over peer memory
+        from hfuse_b200.exchange import BnExchange
+        ex = BnExchange(256)
+        collective = "in-kernel sum of the [256,3] f64 moments over NVLink peer stores"
+
+        def step(i):
+            ex.run_pair(*sets[i % NSETS])
+
+        def drain():
+            pass
+        per_step_launches = 1
+    elif use_dist:
+        # per-GPU moments -> NCCL all-reduce on a side stream (overlaps the next step) -> finalize
+        collective = "NCCL all-reduce of the [256,3] f64 moments on a side stream + finalize kernel"
         comm_stream = torch.cuda.Stream(dev)
         moms = [torch.empty((256, 3), dtype=torch.float64, device=dev) for _ in range(NSETS)]
         for (a, b), m in zip(sets, moms):
             b.moments = m
-        done = [None] * NSETS
         stats = [None] * NSETS
 
         def step(i):
@@ -339,8 +353,7 @@ def run_ours(args):
     if not args.no_graph and args.steps >= GRAPH_STEPS:
         try:
             for k in range(NSETS):
-                if use_dist:
-                    done[k] = None
+                done[k] = None
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                 for i in range(GRAPH_STEPS):
@@ -348,16 +361,14 @@ def run_ours(args):
                 drain()
             graph.replay()
             torch.cuda.synchronize()
-            if use_dist:
-                for k in range(NSETS):
-                    done[k] = None          # events recorded during capture must not be waited on outside
+            for k in range(NSETS):
+                done[k] = None          # events recorded during capture must not be waited on outside
         except Exception as exc:          # capture unsupported here: time direct launches instead
             sys.stderr.write(f"CUDA graph capture failed ({exc!r}); timing direct launches\n")
             graph = None
             torch.cuda.synchronize()
-            if use_dist:
-                for k in range(NSETS):
-                    done[k] = None
+            for k in range(NSETS):
+                done[k] = None
     barrier()
     sampler.start()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -433,8 +444,7 @@ def run_ours(args):
                                "fp32, per GPU", "l2": f"steps rotate over {NSETS} independent buffer sets "
                                f"({NSETS * nbytes >> 20} MiB in total, L2 is 126 MB)",
                    "launch": ("CUDA graph of %d steps, replayed" % GRAPH_STEPS) if graph is not None else "direct launches",
-                   "parallelism": f"batch-sharded x{world}" + (", NCCL all-reduce of [256,3] f64 moments overlapped "
-                                                              "with the next step" if use_dist else "")},
+                   "parallelism": f"batch-sharded x{world}", "collective": collective},
         "gpu_launches": launches,
         "e2e": {"value": round(world * nbytes / e2e_ms / 1e6, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 4)},
@@ -611,6 +621,8 @@ def main():
     ap.add_argument("--count", type=int, default=1 << 24, help="nonces per step with --only cfg3|cfg4")
     ap.add_argument("--dag-items", type=int, default=8_388_608)
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: sum the batch-norm moments inside the fused kernel (peer memory) or with NCCL")
     ap.add_argument("--no-graph", action="store_true", help="time direct launches instead of CUDA-graph replays")
     ap.add_argument("--tune", action="store_true", help="sweep all variants and print the best per kernel / pair")
     ap.add_argument("--graph", action="store_true", help="with --only: replay the launches from a CUDA graph")

@@ -60,6 +60,9 @@ def exported_symbols() -> list[str]:
     """Every function include/hfuse_b200.h declares."""
     names = list(DL_SOLO.values()) + [f"hfuse_{p}_f32" for p in DL_PAIRS]
     names += list(CRYPTO_SOLO.values()) + [f"hfuse_{p}_search" for p in CRYPTO_PAIRS]
+    names += ["hfuse_exchange_create", "hfuse_exchange_local_handle", "hfuse_exchange_connect",
+              "hfuse_exchange_status", "hfuse_exchange_destroy", "hfuse_bnstats_allreduce_f32",
+              "hfuse_upsample_bnstats_allreduce_f32"]
     names += ["hfuse_error_string", "hfuse_version", "hfuse_bnstats_workspace_bytes", "hfuse_bnstats_noalloc_f32",
               "hfuse_bnstats_finalize_f64", "hfuse_hits_reset", "hfuse_hash_batch", "hfuse_tune_set",
               "hfuse_tune_describe", "hfuse_xoshiro256ss_fill"]
@@ -103,6 +106,14 @@ def lib() -> C.CDLL:
     L.hfuse_bnstats_finalize_f64.argtypes = [_p, _i, _f, _p, _p, _p]
     L.hfuse_bnstats_noalloc_f32.restype = _i
     L.hfuse_bnstats_noalloc_f32.argtypes = [_p, _i, _i, _i, _f, _p, _p, _p, _p]
+    L.hfuse_exchange_create.restype, L.hfuse_exchange_create.argtypes = _i, [_i, _i, _i, C.POINTER(_p)]
+    L.hfuse_exchange_local_handle.restype, L.hfuse_exchange_local_handle.argtypes = _i, [_p, C.c_char_p]
+    L.hfuse_exchange_connect.restype, L.hfuse_exchange_connect.argtypes = _i, [_p, C.c_char_p]
+    L.hfuse_exchange_status.restype, L.hfuse_exchange_status.argtypes = _i, [_p, C.POINTER(_i)]
+    L.hfuse_exchange_destroy.restype, L.hfuse_exchange_destroy.argtypes = _i, [_p]
+    L.hfuse_bnstats_allreduce_f32.restype, L.hfuse_bnstats_allreduce_f32.argtypes = _i, BNSTATS + [_p, _p]
+    L.hfuse_upsample_bnstats_allreduce_f32.restype = _i
+    L.hfuse_upsample_bnstats_allreduce_f32.argtypes = UPSAMPLE + BNSTATS + [_p, _p]
     L.hfuse_hits_reset.restype, L.hfuse_hits_reset.argtypes = _i, [_p, _p]
     L.hfuse_hash_batch.restype = _i
     L.hfuse_hash_batch.argtypes = [_i, C.c_char_p, _p, _u32, _u64, _u32, _p, _p, _p]

@@ -1,0 +1,129 @@
+// Batch-norm statistics whose cross-GPU sum happens INSIDE the kernel, over peer memory:
+// the warp that finishes a channel stores its moments into every rank's exchange buffer with
+// plain 8-byte NVLink stores that carry their own validity tag, then collects every rank's
+// row for that channel and folds them in rank order (dl_roles.cuh, BnXchg).  No collective library call, no second launch; the
+// wait for the other ranks is bounded in time and overlaps the other thread range's work.
+// The reference is single-GPU, so none of this has a counterpart there.
+#include "dl_host.cuh"
+
+struct hfuse_exchange {
+    int world = 0, rank = 0, C = 0;
+    size_t bytes = 0;
+    unsigned char* local = nullptr;
+    unsigned char* peer[hfuse::kXchgMaxRanks] = {};
+    bool opened[hfuse::kXchgMaxRanks] = {};
+    unsigned uses[hfuse::kXchgSlots] = {};
+    unsigned long long calls = 0;
+    bool connected = false;
+};
+
+namespace {
+
+constexpr unsigned long long kWaitTimeoutNs = 5ull * 1000 * 1000 * 1000;   // 5 s per exchange wait
+
+int next_use(hfuse_exchange* ex, int C, BnXchg& x) {
+    if (!ex || !ex->connected) return HFUSE_ERR_BAD_ARG;
+    if (C != ex->C) return HFUSE_ERR_BAD_ARG;
+    const unsigned slot = (unsigned)(ex->calls % hfuse::kXchgSlots);
+    ex->uses[slot] += 1;
+    ex->calls += 1;
+    x.world = ex->world;
+    x.rank = ex->rank;
+    x.slot = slot;
+    x.epoch = ex->uses[slot];
+    x.timeout_ns = kWaitTimeoutNs;
+    for (int r = 0; r < hfuse::kXchgMaxRanks; ++r) x.peer[r] = ex->peer[r];
+    return HFUSE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int hfuse_exchange_create(int world, int rank, int channels, hfuse_exchange** out) {
+    if (!out || world < 1 || world > hfuse::kXchgMaxRanks || rank < 0 || rank >= world || channels < 1)
+        return HFUSE_ERR_BAD_ARG;
+    auto* ex = new hfuse_exchange();
+    ex->world = world; ex->rank = rank; ex->C = channels;
+    ex->bytes = sizeof(XchgLayout) + (size_t)hfuse::kXchgSlots * hfuse::kXchgMaxRanks * channels *
+                                         hfuse::kXchgRowWords * sizeof(unsigned long long);
+    if (cudaMalloc(&ex->local, ex->bytes) != cudaSuccess || cudaMemset(ex->local, 0, ex->bytes) != cudaSuccess ||
+        cudaDeviceSynchronize() != cudaSuccess) {
+        (void)cudaGetLastError();
+        if (ex->local) cudaFree(ex->local);
+        delete ex;
+        return HFUSE_ERR_LAUNCH;
+    }
+    ex->peer[rank] = ex->local;
+    ex->connected = (world == 1);
+    *out = ex;
+    return HFUSE_OK;
+}
+
+int hfuse_exchange_local_handle(hfuse_exchange* ex, uint8_t handle[HFUSE_IPC_HANDLE_BYTES]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == HFUSE_IPC_HANDLE_BYTES, "handle size");
+    if (!ex || !handle) return HFUSE_ERR_BAD_ARG;
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, ex->local) != cudaSuccess) { (void)cudaGetLastError(); return HFUSE_ERR_LAUNCH; }
+    memcpy(handle, &h, sizeof h);
+    return HFUSE_OK;
+}
+
+int hfuse_exchange_connect(hfuse_exchange* ex, const uint8_t* handles) {
+    if (!ex || (!handles && ex->world > 1)) return HFUSE_ERR_BAD_ARG;
+    for (int r = 0; r < ex->world; ++r) {
+        if (r == ex->rank || ex->opened[r]) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + (size_t)r * HFUSE_IPC_HANDLE_BYTES, sizeof h);
+        void* p = nullptr;
+        if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess || !p) {
+            (void)cudaGetLastError();
+            return HFUSE_ERR_LAUNCH;
+        }
+        ex->peer[r] = static_cast<unsigned char*>(p);
+        ex->opened[r] = true;
+    }
+    ex->connected = true;
+    return HFUSE_OK;
+}
+
+int hfuse_exchange_status(hfuse_exchange* ex, int* timed_out) {
+    if (!ex || !timed_out) return HFUSE_ERR_BAD_ARG;
+    unsigned st = 0;
+    if (cudaMemcpy(&st, ex->local + offsetof(XchgLayout, status), sizeof st, cudaMemcpyDeviceToHost) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return HFUSE_ERR_LAUNCH;
+    }
+    *timed_out = st != 0;
+    return HFUSE_OK;
+}
+
+int hfuse_exchange_destroy(hfuse_exchange* ex) {
+    if (!ex) return HFUSE_OK;
+    for (int r = 0; r < ex->world; ++r)
+        if (ex->opened[r]) cudaIpcCloseMemHandle(ex->peer[r]);
+    if (ex->local) cudaFree(ex->local);
+    (void)cudaGetLastError();
+    delete ex;
+    return HFUSE_OK;
+}
+
+int hfuse_bnstats_allreduce_f32(HFUSE_BNSTATS_PARAMS(), hfuse_exchange* ex, hfuse_stream_t stream) {
+    BnStatsArgs a;
+    if (int rc = prep_bnstats(BNSTATS_NAMES(), a)) return rc;
+    if (int rc = next_use(ex, C, a.xchg)) return rc;
+    return dispatch_solo<BnStatsXchgRole>("bnstats", kDefaultSolo_bnstats, a, S_(stream));
+}
+
+int hfuse_upsample_bnstats_allreduce_f32(HFUSE_UPSAMPLE_PARAMS(a_), HFUSE_BNSTATS_PARAMS(b_), hfuse_exchange* ex,
+                                         hfuse_stream_t stream) {
+    UpsampleArgs a;
+    BnStatsArgs b;
+    if (int rc = prep_upsample(UPSAMPLE_NAMES(a_), a)) return rc;
+    if (int rc = prep_bnstats(BNSTATS_NAMES(b_), b)) return rc;
+    if (int rc = next_use(ex, b_C, b.xchg)) return rc;
+    return dispatch_pair<UpsampleRole, BnStatsXchgRole>("upsample_bnstats", kDefaultPair_upsample_bnstats, a, b,
+                                                        S_(stream));
+}
+
+}  // extern "C"

@@ -83,6 +83,7 @@ int prep_bnstats(HFUSE_BNSTATS_PARAMS(), BnStatsArgs& a) {
     a.S = 1; a.chunk = 0; a.per_channel = 0; a.per_img = 1; a.div_img = make_fastdiv(1);
     a.vec = (HW % 4) == 0;
     a.ws = workspace; a.ws_bytes = workspace_bytes;
+    a.xchg = BnXchg{};
     return HFUSE_OK;
 }
 

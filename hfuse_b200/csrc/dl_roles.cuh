@@ -553,6 +553,38 @@ struct HistcRole {
 // blocks; otherwise the slice moments go to scratch and the block that takes
 // the last ticket of a channel folds all S of them in slice order, so the
 // result does not depend on arrival order.
+// ---- cross-GPU exchange of the per-channel moments over peer memory -------------------------
+// Every rank owns one exchange buffer and holds peer pointers to all of them.  The warp that
+// has finished channel c sends the channel's (n, sum, sum of squares) to EVERY rank's buffer
+// (row [slot][its rank][c]) as five 8-byte words, each carrying 4 payload bytes and the 4-byte
+// epoch of this use of the slot.  An aligned 8-byte store arrives whole, so a word whose epoch
+// matches holds valid payload: no fence, no counter, no atomic.  The same warp then polls the
+// rows of all ranks for channel c in its OWN buffer (one lane per rank, bounded in time) and
+// folds them in rank order, so all ranks compute the same bits.  Slots rotate and epochs only
+// grow; a rank can run at most one call ahead of the slowest one (its next kernel cannot end
+// before every rank has delivered), so a slot is never overwritten before it has been read.
+constexpr int kXchgMaxRanks = 8;
+constexpr int kXchgSlots = 4;
+constexpr int kXchgRowWords = 6;      // 5 used, padded to 48 bytes
+struct XchgLayout {                   // header of an exchange buffer
+    unsigned status;                  // set to 1 when a wait ran out of time
+    unsigned pad[63];
+    // followed by unsigned long long rows[kXchgSlots][kXchgMaxRanks][C][kXchgRowWords]
+};
+struct BnXchg {
+    int world;                // 0: exchange disabled
+    int rank;
+    unsigned slot;
+    unsigned epoch;           // use count of this slot, never 0 (the buffer starts zeroed)
+    unsigned long long timeout_ns;
+    unsigned char* peer[kXchgMaxRanks];   // exchange buffers of all ranks (peer[rank] is the local one)
+};
+__device__ __forceinline__ volatile unsigned long long* xchg_row(unsigned char* base, int C, unsigned slot, int src,
+                                                                 int c) {
+    unsigned long long* rows = reinterpret_cast<unsigned long long*>(base + sizeof(XchgLayout));
+    return rows + (((size_t)slot * kXchgMaxRanks + src) * C + c) * kXchgRowWords;
+}
+
 struct BnStatsArgs {
     const float* x;       // [N][C][HW]
     int N, C, HW;
@@ -571,6 +603,7 @@ struct BnStatsArgs {
     int vec;              // HW % 4 == 0: 16-byte loads
     size_t ws_bytes;      // size of the caller's scratch buffer (host-side check only)
     void* ws;             // the caller's scratch buffer
+    BnXchg xchg;          // world == 0 unless launched through an exchange entry point
 };
 
 constexpr int kBnMaxSlices = 256;
@@ -646,8 +679,78 @@ struct BnStatsRole {
         }
     }
 
+    // Exchange form of finish(), run by all 32 lanes of one warp with the channel's local
+    // moments in lane 0: send them to every rank, collect every rank's, fold in rank order.
+    static __device__ __forceinline__ void exchange(const Args& a, int c, Moments m, int lane) {
+        const BnXchg& x = a.xchg;
+        const float mean_l = __shfl_sync(0xffffffffu, m.mean, 0);
+        const float m2_l = __shfl_sync(0xffffffffu, m.m2, 0);
+        const double n = (double)a.N * (double)a.HW, mu = (double)mean_l;
+        const unsigned long long s1 = (unsigned long long)__double_as_longlong(n * mu);
+        const unsigned long long s2 = (unsigned long long)__double_as_longlong((double)m2_l + n * mu * mu);
+        const unsigned long long tag = (unsigned long long)x.epoch << 32;
+        if (lane < x.world) {          // lane r sends to rank r: the stores of all ranks go out side by side
+            volatile unsigned long long* row = xchg_row(x.peer[lane], a.C, x.slot, x.rank, c);
+            row[0] = tag | (s1 & 0xffffffffull);
+            row[1] = tag | (s1 >> 32);
+            row[2] = tag | (s2 & 0xffffffffull);
+            row[3] = tag | (s2 >> 32);
+            row[4] = tag | (unsigned long long)(unsigned)((long long)a.N * a.HW);
+        }
+        // lane r collects rank r's row from the local buffer
+        double rs1 = 0.0, rs2 = 0.0, rn = 0.0;
+        bool ok = true;
+        if (lane < x.world) {
+            volatile unsigned long long* row = xchg_row(x.peer[x.rank], a.C, x.slot, lane, c);
+            unsigned long long t0, t1, w[5];
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+            for (;;) {
+#pragma unroll
+                for (int k = 0; k < 5; ++k) w[k] = row[k];
+                bool all = true;
+#pragma unroll
+                for (int k = 0; k < 5; ++k) all &= (unsigned)(w[k] >> 32) == x.epoch;
+                if (all) break;
+                __nanosleep(64);
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+                if (t1 - t0 > x.timeout_ns) { ok = false; break; }
+            }
+            rs1 = __longlong_as_double((long long)((w[0] & 0xffffffffull) | (w[1] << 32)));
+            rs2 = __longlong_as_double((long long)((w[2] & 0xffffffffull) | (w[3] << 32)));
+            rn = (double)(unsigned)(w[4] & 0xffffffffull);
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        double tn = 0.0, t1s = 0.0, t2s = 0.0;
+        for (int r = 0; r < x.world; ++r) {       // rank order: identical bits on every rank
+            tn += __shfl_sync(0xffffffffu, rn, r);
+            t1s += __shfl_sync(0xffffffffu, rs1, r);
+            t2s += __shfl_sync(0xffffffffu, rs2, r);
+        }
+        if (lane == 0) {
+            if (!ok) atomicExch(&reinterpret_cast<XchgLayout*>(x.peer[x.rank])->status, 1u);   // results invalid
+            const double mean = t1s / tn;
+            double var = t2s / tn - mean * mean;
+            if (var < 0.0) var = 0.0;
+            a.mean[c] = (float)mean;
+            a.invstd[c] = (float)(1.0 / sqrt(var + (double)a.eps));
+            if (a.moments) { a.moments[3 * c] = tn; a.moments[3 * c + 1] = t1s; a.moments[3 * c + 2] = t2s; }
+        }
+    }
+
+    // called by all 32 lanes of warp 0 with the channel's folded moments in lane 0
+    template <bool XCHG>
+    static __device__ __forceinline__ void complete(const Args& a, int c, Moments m, int lane) {
+        if (XCHG) exchange(a, c, m, lane);
+        else if (lane == 0) finish(a, c, m);
+    }
+
     template <int T, int BAR>
     static __device__ __forceinline__ void run(const Args& a, const RoleCtx& ctx) {
+        run_impl<T, BAR, false>(a, ctx);
+    }
+
+    template <int T, int BAR, bool XCHG>
+    static __device__ __forceinline__ void run_impl(const Args& a, const RoleCtx& ctx) {
         constexpr int NW = T / 32;
         constexpr int UNROLL = 4;
         static_assert(NW <= 32, "one warp folds the per-warp moments");
@@ -726,7 +829,7 @@ struct BnStatsRole {
             Moments w = (lane < NW) ? Moments{buf[lane], buf[NW + lane], buf[2 * NW + lane]} : Moments{0.f, 0.f, 0.f};
             w = warp_merge(w);
             if (a.S == 1) {
-                if (lane == 0) finish(a, (int)c, w);
+                complete<XCHG>(a, (int)c, w, lane);
                 continue;
             }
             // publish this slice; the block that takes the last ticket folds all slices
@@ -746,12 +849,18 @@ struct BnStatsRole {
                     q = chan_merge(q, Moments{__ldcg(p), __ldcg(p + 1), __ldcg(p + 2)});
                 }
                 q = warp_merge(q);
-                if (lane == 0) {
-                    finish(a, (int)c, q);
-                    a.tickets[c] = 0u;     // ready for the next call
-                }
+                if (lane == 0) a.tickets[c] = 0u;     // ready for the next call
+                complete<XCHG>(a, (int)c, q, lane);
             }
         }
+    }
+};
+
+// The same role with the cross-GPU exchange switched on (fused compute + collective).
+struct BnStatsXchgRole : BnStatsRole {
+    template <int T, int BAR>
+    static __device__ __forceinline__ void run(const Args& a, const RoleCtx& ctx) {
+        BnStatsRole::run_impl<T, BAR, true>(a, ctx);
     }
 };
 

@@ -1,0 +1,67 @@
+"""Cross-GPU batch-norm statistics with the sum inside the kernel (peer memory over NVLink).
+
+    ex = BnExchange(channels)            # one per process, after torch.distributed is initialised
+    ops_a, ops_b = ops.Upsample(...), ops.BnStats(...)
+    ex.run_pair(ops_a, ops_b)            # ONE launch; ops_b.mean / invstd are global statistics
+
+The handles travel through `torch.distributed.all_gather_object`; with a world of one (or
+without torch.distributed) the exchange degenerates to the local buffer, which is how the
+single-GPU tests exercise the same kernel code.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .ops import _stream_ptr
+
+
+class BnExchange:
+    def __init__(self, channels: int, group=None):
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.channels = int(channels)
+        L = _lib.lib()
+        self._h = C.c_void_p()
+        _lib.check(L.hfuse_exchange_create(self.world, self.rank, self.channels, C.byref(self._h)),
+                   "hfuse_exchange_create")
+        if self.world > 1:
+            buf = C.create_string_buffer(64)
+            _lib.check(L.hfuse_exchange_local_handle(self._h, buf), "hfuse_exchange_local_handle")
+            handles = [None] * self.world
+            dist.all_gather_object(handles, buf.raw, group=group)
+            _lib.check(L.hfuse_exchange_connect(self._h, b"".join(handles)), "hfuse_exchange_connect")
+            dist.barrier(group=group)      # every rank has mapped every buffer before the first kernel
+
+    def run(self, bn, stream=None):
+        """Standalone statistics kernel with the in-kernel all-reduce."""
+        _lib.check(_lib.lib().hfuse_bnstats_allreduce_f32(*bn.c_args(), self._h, _stream_ptr(stream)),
+                   "hfuse_bnstats_allreduce_f32")
+        return bn.result()
+
+    def run_pair(self, up, bn, stream=None):
+        """Fused upsample + statistics + in-kernel all-reduce: one launch."""
+        _lib.check(_lib.lib().hfuse_upsample_bnstats_allreduce_f32(*up.c_args(), *bn.c_args(), self._h,
+                                                                   _stream_ptr(stream)),
+                   "hfuse_upsample_bnstats_allreduce_f32")
+        return up.result(), bn.result()
+
+    def timed_out(self) -> bool:
+        flag = C.c_int(0)
+        _lib.check(_lib.lib().hfuse_exchange_status(self._h, C.byref(flag)), "hfuse_exchange_status")
+        return bool(flag.value)
+
+    def close(self):
+        if self._h:
+            torch.cuda.synchronize()
+            _lib.lib().hfuse_exchange_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -158,6 +158,31 @@ HFUSE_API int hfuse_histc_bnstats_f32(HFUSE_HISTC_PARAMS(a_), HFUSE_BNSTATS_PARA
                                       hfuse_stream_t stream);                         /* ml_fusion.yaml:37-40 */
 
 /* ---------------------------------------------------------------------------------------
+ * Multi-GPU batch-norm statistics with the cross-GPU sum inside the kernel (no counterpart
+ * in the reference, which is single-GPU).  One process per GPU; each creates an exchange
+ * object (a small device buffer), publishes its IPC handle, collects every rank's handle
+ * (any transport: torch.distributed, MPI, a file) and connects.  The *_allreduce entry
+ * points then behave like their plain namesakes except that mean / invstd (and `moments`)
+ * are the statistics over ALL ranks' batches: the statistics thread range stores each
+ * channel's moments into every rank's buffer over NVLink and folds all ranks' rows once the
+ * last one has arrived.  Rules: every rank makes the same sequence of calls on one exchange
+ * object; calls on one object go to one stream; the in-kernel wait for the other ranks gives
+ * up after 5 s and raises the flag hfuse_exchange_status reports (results are then invalid).
+ * ------------------------------------------------------------------------------------- */
+#define HFUSE_IPC_HANDLE_BYTES 64
+#define HFUSE_MAX_RANKS 8
+typedef struct hfuse_exchange hfuse_exchange;
+HFUSE_API int hfuse_exchange_create(int world, int rank, int channels, hfuse_exchange** out);
+HFUSE_API int hfuse_exchange_local_handle(hfuse_exchange* ex, uint8_t handle[HFUSE_IPC_HANDLE_BYTES]);
+/* handles: world x HFUSE_IPC_HANDLE_BYTES bytes in rank order (host memory); the own entry is ignored */
+HFUSE_API int hfuse_exchange_connect(hfuse_exchange* ex, const uint8_t* handles);
+HFUSE_API int hfuse_exchange_status(hfuse_exchange* ex, int* timed_out);   /* synchronises the device */
+HFUSE_API int hfuse_exchange_destroy(hfuse_exchange* ex);
+HFUSE_API int hfuse_bnstats_allreduce_f32(HFUSE_BNSTATS_PARAMS(), hfuse_exchange* ex, hfuse_stream_t stream);
+HFUSE_API int hfuse_upsample_bnstats_allreduce_f32(HFUSE_UPSAMPLE_PARAMS(a_), HFUSE_BNSTATS_PARAMS(b_),
+                                                   hfuse_exchange* ex, hfuse_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
  * Crypto nonce searches.
  *
  * Reference kernels (configs/crypto_kernels.yaml:1-32, signatures in

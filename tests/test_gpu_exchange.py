@@ -1,0 +1,95 @@
+"""The in-kernel cross-GPU sum of the batch-norm moments (hfuse_*_allreduce_f32).
+
+With one GPU the exchange degenerates to the local buffer: the same device code runs (rows
+delivered, counters bumped, the last block waits and folds), so slot rotation and counter
+arithmetic are covered on any box.  The 2-rank test needs two GPUs and is skipped otherwise;
+its ranks are child processes that talk over gloo only to swap the IPC handles.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from hfuse_b200 import ops
+from oracle import dl
+
+pytestmark = pytest.mark.gpu
+
+
+def test_world_of_one_matches_plain_kernels_over_many_calls(dev):
+    from hfuse_b200.exchange import BnExchange
+    g = torch.Generator().manual_seed(21)
+    shapes = [(8, 32, 14, 14), (64, 4, 32, 32)]              # one slice per channel, and many slices per channel
+    for shape in shapes:
+        ex = BnExchange(shape[1])
+        for it in range(10):                                  # more calls than slots: counters keep growing
+            x = (0.5 + 2.0 * torch.randn(*shape, generator=g))
+            op = ops.BnStats(x.to(dev), 1e-5, want_moments=True)
+            ex.run(op)
+            mr, sr = dl.bnstats_f64(x, 1e-5)
+            np.testing.assert_allclose(op.mean.cpu().double().numpy(), mr.numpy(), rtol=1e-5)
+            np.testing.assert_allclose(op.invstd.cpu().double().numpy(), sr.numpy(), rtol=1e-5)
+            n = x.numel() // x.shape[1]
+            np.testing.assert_allclose(op.moments[:, 0].cpu().numpy(), n)
+        up = torch.rand(2, 4, 12, 16, generator=g)
+        a, b = ops.Upsample(up.to(dev), scale_factor=2), ops.BnStats(x.to(dev), 1e-5)
+        ex.run_pair(a, b)
+        assert np.array_equal(a.out.cpu().numpy(), dl.upsample_numpy(up.numpy(), 24, 32))
+        np.testing.assert_allclose(b.mean.cpu().double().numpy(), mr.numpy(), rtol=1e-5)
+        assert not ex.timed_out()
+        ex.close()
+
+
+def _rank_main(rank, world, port, ret):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from hfuse_b200 import sharding
+        from hfuse_b200.exchange import BnExchange
+        dev = torch.device("cuda", rank)
+        ex = BnExchange(24)
+        ok = True
+        g = torch.Generator().manual_seed(33)
+        for it in range(9):
+            x = 0.5 + 2.0 * torch.randn(8, 24, 10, 10, generator=g)         # same tensor on every rank
+            mine = sharding.shard_batch(x, rank, world).contiguous().to(dev)
+            up = torch.rand(2, 3, 8, 8, generator=g)
+            a, b = ops.Upsample(up.to(dev), scale_factor=2), ops.BnStats(mine, 1e-5)
+            if it % 2:
+                ex.run_pair(a, b)
+                ok &= np.array_equal(a.out.cpu().numpy(), dl.upsample_numpy(up.numpy(), 16, 16))
+            else:
+                ex.run(b)
+            mr, sr = dl.bnstats_f64(x, 1e-5)                                  # statistics of the WHOLE batch
+            ok &= np.allclose(b.mean.cpu().double().numpy(), mr.numpy(), rtol=1e-5, atol=0)
+            ok &= np.allclose(b.invstd.cpu().double().numpy(), sr.numpy(), rtol=1e-5, atol=0)
+        ok &= not ex.timed_out()
+        # all ranks hold identical bits
+        mine_bits = b.mean.cpu()
+        got = [None] * world
+        dist.all_gather_object(got, mine_bits)
+        ok &= all(torch.equal(got[0], t) for t in got)
+        ret[rank] = bool(ok)
+        dist.barrier()
+        ex.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_sum_over_nvlink(dev):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = 29700 + os.getpid() % 1000
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+        assert p.exitcode == 0
+    assert ret[0] and ret[1]
