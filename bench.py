@@ -400,6 +400,14 @@ def run_ours(args):
         b.moments = None
     t_kernel = graph_region(torch, lambda i: ops.run_pair(*sets[i % NSETS]), NSETS, max(args.steps, 120), 3)
 
+    # context for the roofline fraction: a plain device copy that moves the same number of bytes
+    # (half read, half written), timed the same way, same rotation depth
+    half = nbytes // 2 // 4
+    csrc = [torch.empty(half, dtype=torch.float32, device=dev).normal_() for _ in range(NSETS)]
+    cdst = [torch.empty(half, dtype=torch.float32, device=dev) for _ in range(NSETS)]
+    t_copy = graph_region(torch, lambda i: cdst[i % NSETS].copy_(csrc[i % NSETS]), NSETS, 120, 3)
+    del csrc, cdst
+
     # ---- end to end through the C ABI with host buffers (pinned), copies inside the timed region
     w = workloads.config1()
     h_up, h_bn = w["up"].pin_memory(), w["bn"].pin_memory()
@@ -451,7 +459,8 @@ def run_ours(args):
         "roofline": {"bound": "hbm", "achieved": round(nbytes / t_kernel / 1e6, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(nbytes / t_kernel / 1e6 / peak, 4), "traffic": NCU_TRAFFIC_BYTES,
                      "peak_kind": peak_kind, "kernel": "fused_kernel<UpsampleRole,BnStatsRole>",
-                     "kernel_us": round(t_kernel * 1e3, 2)},
+                     "kernel_us": round(t_kernel * 1e3, 2),
+                     "same_bytes_device_copy_us": round(t_copy * 1e3, 2)},
         "clocks": clocks,
     }
     if rank == 0 and world == 1:
@@ -460,10 +469,55 @@ def run_ours(args):
                                 "kind": "port", "sample": "5 full passes of configuration 1 with PyTorch CPU operators"}
         if not args.no_extras:
             line["pairs"] = extras(torch, ops, crypto, workloads, dev, max(20, min(args.steps, 200)), 3, peak, barrier)
+    if use_dist and not args.no_extras:
+        sharded = crypto_sharded(torch, crypto, sharding, workloads, dev, rank, world, barrier)
+        if rank == 0:
+            line["crypto_sharded"] = sharded
     if rank == 0:
         print(json.dumps(line), flush=True)
     if use_dist:
         shutdown(torch, graph)
+
+
+def crypto_sharded(torch, crypto, sharding, workloads, dev, rank, world, barrier):
+    """Configurations 3 and 4 with the nonce range cut into one contiguous shard per GPU (strong
+    scaling: the total sweep is fixed), DAG replicated.  Time = max over ranks of the device time of
+    the rank's fused launch; hit lists are gathered and merged on the host."""
+    import torch.distributed as dist
+    out = {}
+
+    def timed(fn):
+        fn()                                   # warm-up (also builds the occupancy cache)
+        torch.cuda.synchronize()
+        barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([s.elapsed_time(e)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    c3 = workloads.config3()
+    st, n = sharding.shard_nonces(c3["start"], c3["count"], rank, world)
+    a = crypto.Blake256(c3["blake_header"], st, n, c3["target"])
+    b = crypto.Sha256d(c3["sha_header"], st, n, c3["target"])
+    ms = timed(lambda: crypto.run_pair(a, b))
+    hits_a, hits_b = sharding.gather_hits(a.result()[1]), sharding.gather_hits(b.result()[1])
+    out["cfg3_blake256_sha256d"] = {"nonces_each_total": c3["count"], "fused_ms": round(ms, 2),
+                                    "GH_per_s_each": round(c3["count"] / ms / 1e6, 3),
+                                    "hits": [len(hits_a), len(hits_b)], "blake256_nonces": [h[0] for h in hits_a]}
+    c4 = workloads.config4(dev)
+    st, n = sharding.shard_nonces(c4["start"], c4["count"], rank, world)
+    s_ = crypto.Sia(c4["sia_header"], st, n, c4["target"])
+    e_ = crypto.Ethash(c4["dag"], c4["header_hash"], st, n, c4["target"])
+    ms = timed(lambda: crypto.run_pair(s_, e_))
+    hits_s, hits_e = sharding.gather_hits(s_.result()[1]), sharding.gather_hits(e_.result()[1])
+    out["cfg4_sia_ethash"] = {"nonces_each_total": c4["count"], "fused_ms": round(ms, 2),
+                              "ethash_MH_per_s": round(c4["count"] / ms / 1e3, 1),
+                              "sia_GH_per_s": round(c4["count"] / ms / 1e6, 3), "hits": [len(hits_s), len(hits_e)]}
+    return out
 
 
 def shutdown(torch, graph):
@@ -485,10 +539,10 @@ def shutdown(torch, graph):
 
 
 # DRAM bytes (read + write) per launch of the headline fused kernel from the committed ncu
-# capture (profiles/fused_upsample_bnstats_cfg1.md): 51,438,848 read + 46,592,512 written.  It is
+# capture (profiles/fused_upsample_bnstats_cfg1.md): 51.44 MB read + 46.77 MB written.  It is
 # below the algorithmic 154,142,720 B because part of the output is still dirty in L2 when an
 # isolated launch ends.
-NCU_TRAFFIC_BYTES = 98_031_360
+NCU_TRAFFIC_BYTES = 98213120
 
 
 def run_only(args, torch, ops, crypto, workloads, dev):
