@@ -79,5 +79,34 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+TORCH_EXT = os.path.join(HERE, "_torch_ext.so")
+
+
+def build_torch_ext(force: bool = False) -> str:
+    """The PyTorch extension (torch.ops.hfuse_b200.*): one host-only C++ file compiled with g++
+    against the installed torch headers and linked to libhfuse_b200.so beside it."""
+    import torch
+    from torch.utils import cpp_extension as ce
+    src = os.path.join(CSRC, "torch_ext.cpp")
+    hdr = os.path.join(HERE, "..", "include", "hfuse_b200.h")
+    if not force and os.path.exists(TORCH_EXT) and os.path.getmtime(TORCH_EXT) >= max(
+            os.path.getmtime(src), os.path.getmtime(hdr)):
+        return TORCH_EXT
+    build()
+    tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cuda_inc = os.path.join(os.path.dirname(os.path.dirname(_nvcc())), "include")
+    cmd = ["/usr/bin/g++", "-O2", "-std=c++17", "-fPIC", "-shared", src, "-o", TORCH_EXT,
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}", "-DTORCH_EXTENSION_NAME=_torch_ext",
+           *[f"-I{p}" for p in ce.include_paths()], f"-I{cuda_inc}",
+           f"-L{tlib}", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch",
+           f"-L{HERE}", "-lhfuse_b200", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{tlib}"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"torch extension build failed:\n{r.stdout}\n{r.stderr[-4000:]}")
+    return TORCH_EXT
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--torch-ext" in sys.argv:
+        print(build_torch_ext(force="--force" in sys.argv))

@@ -72,3 +72,14 @@ def test_ops_refuse_cpu_tensors():
     from hfuse_b200 import ops
     with pytest.raises(RuntimeError, match="no CPU path"):
         ops.im2col(torch.zeros(1, 1, 4, 4), 3, 1)
+
+
+def test_torch_extension_registers_every_pair_and_refuses_cpu_tensors():
+    import pytest
+    import torch
+    from hfuse_b200 import torch_ops  # noqa: F401
+    for name in list(_lib.DL_PAIRS) + ["im2col", "max_pool2d_with_indices", "batch_norm_stats", "upsample_bilinear2d",
+                                       "histc"]:
+        assert hasattr(torch.ops.hfuse_b200, name), name
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        torch.ops.hfuse_b200.histc(torch.zeros(4), 4, 0.0, 1.0)
