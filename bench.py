@@ -179,10 +179,28 @@ def build_dl_sets(torch, ops, workloads, cfg, dev, nsets):
 def measure_dl_pair(torch, ops, sets, steps, warmup, barrier):
     n = len(sets)
     t_f = graph_region(torch, lambda i: ops.run_pair(*sets[i % n]), n, steps, warmup)
+    t_v = vertical_time(torch, ops, sets, steps, warmup)
     t_b = graph_region(torch, lambda i: ops.run_back_to_back(*sets[i % n]), n, steps, warmup)
     t_a = graph_region(torch, lambda i: ops.run(sets[i % n][0]), n, steps, warmup)
     t_2 = graph_region(torch, lambda i: ops.run(sets[i % n][1]), n, steps, warmup)
-    return t_f, t_b, t_a, t_2
+    return t_f, t_b, t_a, t_2, t_v
+
+
+def vertical_time(torch, ops, sets, steps, warmup):
+    """Best of the vertical-fusion variants (same threads run both bodies), the reference's vfuse column."""
+    from hfuse_b200 import _lib
+    name = ops.pair_name(*sets[0])
+    n, best = len(sets), None
+    try:
+        for v, d in enumerate(_lib.tune_variants(name)):
+            if ":0:" not in d:
+                continue
+            _lib.tune_set(name, v, 0)
+            t = graph_region(torch, lambda i: ops.run_pair(*sets[i % n]), n, steps, warmup)
+            best = t if best is None else min(best, t)
+    finally:
+        _lib.tune_set(name, -1, 0)
+    return best
 
 
 def extras(torch, ops, crypto, workloads, dev, steps, warmup, peak, barrier):
@@ -190,9 +208,10 @@ def extras(torch, ops, crypto, workloads, dev, steps, warmup, peak, barrier):
     out = {}
     for cfg in (0, 1, 2):
         name, sets, nbytes = build_dl_sets(torch, ops, workloads, cfg, dev, 4)
-        tf, tb, ta, t2 = measure_dl_pair(torch, ops, sets, steps, warmup, barrier)
+        tf, tb, ta, t2, tv = measure_dl_pair(torch, ops, sets, steps, warmup, barrier)
         out[f"cfg{cfg}_{name}"] = {
             "fused_us": round(tf * 1e3, 2), "back_to_back_us": round(tb * 1e3, 2),
+            "vertical_fusion_us": round(tv * 1e3, 2),
             "first_alone_us": round(ta * 1e3, 2), "second_alone_us": round(t2 * 1e3, 2),
             "speedup_vs_back_to_back": round(tb / tf, 3), "GB_per_s": round(nbytes / tf / 1e6, 1),
             "frac_of_hbm_peak": round(nbytes / tf / 1e6 / peak, 3), "algorithmic_bytes": nbytes}
@@ -286,6 +305,8 @@ def run_ours(args):
         return run_only(args, torch, ops, crypto, workloads, dev)
     if args.tune:
         return run_tune(args, torch, ops, crypto, workloads, dev)
+    if args.study:
+        return run_study(args, torch, ops, crypto, workloads, dev)
 
     NSETS = 6
     name, sets, nbytes = build_dl_sets(torch, ops, workloads, 1, dev, NSETS)
@@ -618,9 +639,12 @@ def run_tune(args, torch, ops, crypto, workloads, dev):
             _lib.tune_set(name, v, 0)
             times[d] = round(graph_region(torch, lambda i: ops.run_pair(*sets[i % NS]), NS, steps, 3) * 1e3, 2)
         _lib.tune_set(name, -1, 0)
-        best = min(times, key=times.get)
+        horiz = {d: t for d, t in times.items() if ":0:" not in d}      # "T:0:mb" = vertical fusion
+        vert = {d: t for d, t in times.items() if ":0:" in d}
+        best = min(horiz, key=horiz.get)
         result["pair"][name] = {"best": list(times).index(best), "variant": best, "us": times[best],
                                 "back_to_back_us": round(t_b2b, 2), "speedup": round(t_b2b / times[best], 3),
+                                "vertical_best": min(vert, key=vert.get), "vertical_us": min(vert.values()),
                                 "all": times}
         del sets
         torch.cuda.empty_cache()
@@ -664,6 +688,71 @@ def run_tune(args, torch, ops, crypto, workloads, dev):
     print(json.dumps(result))
 
 
+def run_study(args, torch, ops, crypto, workloads, dev):
+    """Speedup of the fused pair over back-to-back as a function of the ratio of the two
+    standalone times (the reference's Fig. 7 scatter, scripts/analyze_nvprof.py:272-273,483-648):
+    one half keeps its benchmark size, the other half's batch (or nonce count) is scaled."""
+    from hfuse_b200 import _lib
+    NS, steps = 3, 36
+    g = torch.Generator().manual_seed(7)
+
+    def mk(key, scale):
+        if key == "im2col":
+            return ops.Im2col((torch.rand(max(1, int(16 * scale)), 64, 56, 56, generator=g) * 2 - 1).to(dev), 3, 1, 1, 1)
+        if key == "maxpool":
+            return ops.MaxPool((torch.rand(max(1, int(16 * scale)), 64, 112, 112, generator=g) * 2 - 1).to(dev), 2, 2)
+        if key == "bnstats":
+            return ops.BnStats((0.5 + 2 * torch.randn(max(1, int(32 * scale)), 256, 28, 28, generator=g)).to(dev), 1e-5)
+        if key == "upsample":
+            return ops.Upsample(torch.rand(max(1, int(16 * scale)), 128, 56, 56, generator=g).to(dev), scale_factor=2)
+        return ops.Histc(torch.randn(int((1 << 24) * scale) // 4 * 4, generator=g).to(dev), 256, -4.0, 4.0)
+
+    rows = []
+    for name in ("im2col_maxpool", "upsample_bnstats", "im2col_histc", "histc_maxpool", "maxpool_bnstats"):
+        ka, kb = _lib.DL_PAIRS[name]
+        for scale in (0.25, 0.5, 1.0, 2.0, 4.0):
+            sets = [(mk(ka, 1.0), mk(kb, scale)) for _ in range(NS)]
+            ta = graph_region(torch, lambda i: ops.run(sets[i % NS][0]), NS, steps, 3)
+            tb = graph_region(torch, lambda i: ops.run(sets[i % NS][1]), NS, steps, 3)
+            t2 = graph_region(torch, lambda i: ops.run_back_to_back(*sets[i % NS]), NS, steps, 3)
+            best_h, best_v = (None, None), (None, None)
+            for v, d in enumerate(_lib.tune_variants(name)):
+                _lib.tune_set(name, v, 0)
+                t = graph_region(torch, lambda i: ops.run_pair(*sets[i % NS]), NS, steps, 3)
+                if ":0:" in d:
+                    best_v = (t, d) if best_v[0] is None or t < best_v[0] else best_v
+                else:
+                    best_h = (t, d) if best_h[0] is None or t < best_h[0] else best_h
+            _lib.tune_set(name, -1, 0)
+            rows.append({"pair": name, "second_half_scale": scale, "first_us": round(ta * 1e3, 2),
+                         "second_us": round(tb * 1e3, 2), "ratio_first_over_second": round(ta / tb, 3),
+                         "back_to_back_us": round(t2 * 1e3, 2), "horizontal_us": round(best_h[0] * 1e3, 2),
+                         "horizontal_variant": best_h[1], "vertical_us": round(best_v[0] * 1e3, 2),
+                         "speedup_horizontal": round(t2 / best_h[0], 3), "speedup_vertical": round(t2 / best_v[0], 3)})
+            del sets
+            torch.cuda.empty_cache()
+    c3, c4 = workloads.config3(), workloads.config4(dev)
+    none = lambda: None
+    NE = 1 << 22
+    for mult in (1, 4, 16, 64):
+        a = crypto.Sia(c4["sia_header"], 0, NE * mult, c4["target"])
+        b = crypto.Ethash(c4["dag"], c4["header_hash"], 0, NE, c4["target"])
+        ta = time_region(torch, lambda i: crypto.run(a), 2, 1, none) / 2
+        tb = time_region(torch, lambda i: crypto.run(b), 2, 1, none) / 2
+        t2 = time_region(torch, lambda i: crypto.run_back_to_back(a, b), 2, 1, none) / 2
+        best = (None, None)
+        for v, d in enumerate(_lib.tune_variants("sia_ethash")):
+            _lib.tune_set("sia_ethash", v, 0)
+            t = time_region(torch, lambda i: crypto.run_pair(a, b), 2, 1, none) / 2
+            best = (t, d) if best[0] is None or t < best[0] else best
+        _lib.tune_set("sia_ethash", -1, 0)
+        rows.append({"pair": "sia_ethash", "sia_nonces_per_ethash_nonce": mult, "first_ms": round(ta, 3),
+                     "second_ms": round(tb, 3), "ratio_first_over_second": round(ta / tb, 3),
+                     "back_to_back_ms": round(t2, 3), "horizontal_ms": round(best[0], 3), "horizontal_variant": best[1],
+                     "speedup_horizontal": round(t2 / best[0], 3)})
+    print(json.dumps({"study": rows}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -679,6 +768,7 @@ def main():
                     help="N > 1: sum the batch-norm moments inside the fused kernel (peer memory) or with NCCL")
     ap.add_argument("--no-graph", action="store_true", help="time direct launches instead of CUDA-graph replays")
     ap.add_argument("--tune", action="store_true", help="sweep all variants and print the best per kernel / pair")
+    ap.add_argument("--study", action="store_true", help="speedup vs ratio of the standalone times, as JSON")
     ap.add_argument("--graph", action="store_true", help="with --only: replay the launches from a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":

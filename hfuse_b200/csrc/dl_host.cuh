@@ -142,7 +142,9 @@ template <class A> int pre_launch(const A&, cudaStream_t) { return HFUSE_OK; }
     X(5, 768, 256, 1) X(6, 256, 768, 1) X(7, 640, 384, 1) X(8, 384, 640, 1) X(9, 512, 256, 1)       \
     X(10, 256, 512, 1) X(11, 128, 128, 4) X(12, 128, 128, 6) X(13, 896, 128, 1) X(14, 128, 896, 1)  \
     X(15, 512, 256, 2) X(16, 256, 512, 2)
-constexpr int kDlPairVariants = 17;
+// vertical fusion (the reference's vfuse presets): (index, T, minBlocks/SM), described as "T:0:minBlocks"
+#define DL_VPAIR_VARIANTS(X) X(17, 512, 2) X(18, 1024, 1) X(19, 256, 4)
+constexpr int kDlPairVariants = 20;
 
 #define DL_SOLO_VARIANTS(X) X(0, 256, 4) X(1, 256, 8) X(2, 512, 2) X(3, 128, 8) X(4, 512, 4) X(5, 1024, 1) X(6, 128, 16)
 constexpr int kDlSoloVariants = 7;
@@ -157,6 +159,10 @@ int dispatch_pair(const char* name, int default_variant, typename RA::Args a, ty
 #define X(I, TA, TB, MB) \
     case I: return launch_pair<RA, RB, TA, TB, MB>(a, b, t.blocks_per_sm, s);
         DL_PAIR_VARIANTS(X)
+#undef X
+#define X(I, T, MB) \
+    case I: return launch_vpair<RA, RB, T, MB>(a, b, t.blocks_per_sm, s);
+        DL_VPAIR_VARIANTS(X)
 #undef X
     }
     return HFUSE_ERR_BAD_ARG;
@@ -181,6 +187,10 @@ int describe_dl_pair(int v, char* buf, size_t n) {
 #define X(I, TA, TB, MB) \
     case I: snprintf(buf, n, "%d:%d:%d", TA, TB, MB); return kDlPairVariants;
         DL_PAIR_VARIANTS(X)
+#undef X
+#define X(I, T, MB) \
+    case I: snprintf(buf, n, "%d:0:%d", T, MB); return kDlPairVariants;
+        DL_VPAIR_VARIANTS(X)
 #undef X
     }
     return HFUSE_ERR_BAD_ARG;

@@ -37,6 +37,21 @@ fused_kernel(const __grid_constant__ typename RoleA::Args a, const __grid_consta
     }
 }
 
+// Vertical fusion, the reference's `vfuse` presets (tools/llvm-smart-fuser/main.cpp:182-193,
+// include/KernelFusion.h:75-78): every thread range starts at 0, i.e. the SAME threads run
+// body 1 and then body 2, block = max(T1, T2).  Kept as the third column of the comparison
+// (standalone back to back, vertical, horizontal), like the reference's own analysis.
+template <class RoleA, class RoleB, int T, int MINB>
+__global__ void __launch_bounds__(T, MINB)
+vfused_kernel(const __grid_constant__ typename RoleA::Args a, const __grid_constant__ typename RoleB::Args b) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    RoleCtx ctx{(int)threadIdx.x, (int)blockIdx.x, (int)gridDim.x, smem};
+    RoleA::template run<T, 1>(a, ctx);
+    // body 2 reuses the shared memory: everyone must be done with body 1's first
+    role_sync<2, T>();
+    RoleB::template run<T, 1>(b, ctx);
+}
+
 // Fused pair of two work-queue roles (the nonce searches).  The block is still split into
 // role A's and role B's thread ranges; each range drains its own queue first and then helps
 // with the other one, so no range idles while the other still has nonces left.

@@ -112,6 +112,24 @@ int launch_pair(typename RA::Args a, typename RB::Args b, int blocks_per_sm, cud
     return check_launch();
 }
 
+// ---- the same threads run both roles one after the other (vertical fusion) ------------------
+template <class RA, class RB, int T, int MINB>
+int launch_vpair(typename RA::Args a, typename RB::Args b, int blocks_per_sm, cudaStream_t s) {
+    DeviceFacts f;
+    if (int rc = device_facts(f)) return rc;
+    auto kern = vfused_kernel<RA, RB, T, MINB>;
+    if (int rc = RA::plan(a, T, f.sms * MINB)) return rc;
+    if (int rc = RB::plan(b, T, f.sms * MINB)) return rc;
+    const int sa = RA::smem_bytes(a, T), sb = RB::smem_bytes(b, T);
+    const size_t smem = (size_t)(sa > sb ? sa : sb);
+    const int bps = blocks_per_sm > 0 ? blocks_per_sm : resident_blocks((const void*)kern, T, smem);
+    const int grid = f.sms * bps;
+    if (int rc = RA::plan(a, T, grid)) return rc;
+    if (int rc = RB::plan(b, T, grid)) return rc;
+    kern<<<grid, T, smem, s>>>(a, b);
+    return check_launch();
+}
+
 // chunk of nonces a warp takes from a queue at a time: about 16 chunks per resident warp,
 // a multiple of 32, at least 128, and large enough that the 32-bit cursor cannot wrap
 inline unsigned queue_chunk(unsigned long long count, long long warps) {
