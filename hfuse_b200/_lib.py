@@ -63,6 +63,7 @@ def exported_symbols() -> list[str]:
     names += ["hfuse_exchange_create", "hfuse_exchange_local_handle", "hfuse_exchange_connect",
               "hfuse_exchange_status", "hfuse_exchange_destroy", "hfuse_bnstats_allreduce_f32",
               "hfuse_upsample_bnstats_allreduce_f32"]
+    names += ["hfuse_ethash_make_cache", "hfuse_ethash_generate_dag"]
     names += ["hfuse_error_string", "hfuse_version", "hfuse_bnstats_workspace_bytes", "hfuse_bnstats_noalloc_f32",
               "hfuse_bnstats_finalize_f64", "hfuse_hits_reset", "hfuse_hash_batch", "hfuse_tune_set",
               "hfuse_tune_describe", "hfuse_xoshiro256ss_fill"]
@@ -114,6 +115,9 @@ def lib() -> C.CDLL:
     L.hfuse_bnstats_allreduce_f32.restype, L.hfuse_bnstats_allreduce_f32.argtypes = _i, BNSTATS + [_p, _p]
     L.hfuse_upsample_bnstats_allreduce_f32.restype = _i
     L.hfuse_upsample_bnstats_allreduce_f32.argtypes = UPSAMPLE + BNSTATS + [_p, _p]
+    L.hfuse_ethash_make_cache.restype, L.hfuse_ethash_make_cache.argtypes = _i, [C.c_char_p, _u32, _p]
+    L.hfuse_ethash_generate_dag.restype = _i
+    L.hfuse_ethash_generate_dag.argtypes = [_p, _u32, _p, _u32, _u32, _p]
     L.hfuse_hits_reset.restype, L.hfuse_hits_reset.argtypes = _i, [_p, _p]
     L.hfuse_hash_batch.restype = _i
     L.hfuse_hash_batch.argtypes = [_i, C.c_char_p, _p, _u32, _u64, _u32, _p, _p, _p]

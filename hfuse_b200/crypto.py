@@ -138,3 +138,26 @@ def hash_batch(kind: str, header: bytes, start: int, count: int, dag: torch.Tens
         dag.numel() // 128 if dag is not None else 0, start & (2 ** 64 - 1), count, out.data_ptr(),
         mix.data_ptr() if mix is not None else None, _stream_ptr()), "hfuse_hash_batch")
     return out.cpu().numpy(), (mix.cpu().numpy() if mix is not None else None)
+
+
+def make_cache(seed: bytes, cache_nodes: int) -> np.ndarray:
+    """ethash light cache (cache_nodes x 64 bytes), built on the host: it is a sequential chain."""
+    if len(seed) != 32:
+        raise ValueError("seed must be 32 bytes")
+    out = np.empty(64 * cache_nodes, dtype=np.uint8)
+    _lib.check(_lib.lib().hfuse_ethash_make_cache(bytes(seed), cache_nodes, out.ctypes.data), "hfuse_ethash_make_cache")
+    return out
+
+
+def generate_dag(cache: torch.Tensor, n_nodes: int, chunks: int = 1) -> torch.Tensor:
+    """DAG of n_nodes 64-byte nodes from a device-resident cache, in `chunks` launches
+    (the reference's binary uses 16).  Returns a uint8 tensor of n_nodes * 64 bytes."""
+    if not cache.is_cuda or cache.dtype != torch.uint8 or cache.numel() % 64:
+        raise ValueError("cache must be a CUDA uint8 tensor of n*64 bytes")
+    dag = torch.empty(n_nodes * 64, dtype=torch.uint8, device=cache.device)
+    per = (n_nodes + chunks - 1) // chunks
+    for first in range(0, n_nodes, per):
+        cnt = min(per, n_nodes - first)
+        _lib.check(_lib.lib().hfuse_ethash_generate_dag(cache.data_ptr(), cache.numel() // 64, dag.data_ptr(), first,
+                                                        cnt, _stream_ptr()), "hfuse_ethash_generate_dag")
+    return dag

@@ -249,6 +249,16 @@ HFUSE_API int hfuse_blake256_sia_search(HFUSE_BLAKE256_PARAMS(a_), HFUSE_SIA_PAR
 HFUSE_API int hfuse_sha256d_sia_search(HFUSE_SHA256D_PARAMS(a_), HFUSE_SIA_PARAMS(b_),
                                        hfuse_stream_t stream);                        /* crypto_fusion.yaml:21-24 */
 
+/* ethash DAG generation — the step before the search (reference: 16 launches of
+ * ethash_calculate_dag_item ahead of every search, scripts/data/miner.json:10052).  Public
+ * ethash specification: the light cache (cache_nodes x 64 bytes, host memory, sequential
+ * Keccak-512 chain plus three mixing rounds) is built on the host; DAG node i (64 bytes) =
+ * Keccak-512 over 256 FNV-mixed cache parents.  Nodes [first_node, first_node + node_count)
+ * are written at dag + 64 * node (device); a 128-byte DAG item of the search is two nodes. */
+HFUSE_API int hfuse_ethash_make_cache(const uint8_t seed32[32], uint32_t cache_nodes, void* host_cache);
+HFUSE_API int hfuse_ethash_generate_dag(const void* cache, uint32_t cache_nodes, void* dag, uint32_t first_node,
+                                        uint32_t node_count, hfuse_stream_t stream);
+
 /* Single-hash device evaluation for tests: digest (and ethash mix) of `count` consecutive
  * nonces, written to out32[count][32] (and mix32[count][32], may be NULL unless kind 3).
  * kind: 0 BLAKE-256, 1 SHA-256d, 2 Sia BLAKE2b, 3 ethash (header = header_hash32). */

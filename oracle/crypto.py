@@ -44,6 +44,9 @@ def lib() -> ctypes.CDLL:
                                        ctypes.c_void_p, ctypes.c_size_t]
         _lib.oracle_ethash_hashimoto.argtypes = [ctypes.c_void_p, ctypes.c_uint32, u8p, ctypes.c_uint64,
                                                  ctypes.c_void_p, ctypes.c_void_p]
+        _lib.oracle_ethash_mkcache.argtypes = [u8p, ctypes.c_uint32, ctypes.c_void_p]
+        _lib.oracle_ethash_dataset.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32,
+                                               ctypes.c_void_p]
         _lib.oracle_blake2b.argtypes = [u8p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_size_t]
         for name in ("oracle_sha256", "oracle_blake256"):
             getattr(_lib, name).argtypes = [u8p, ctypes.c_size_t, ctypes.c_void_p]
@@ -111,6 +114,20 @@ def hashimoto(dag: np.ndarray, header_hash: bytes, nonce: int):
     mix, res = _out(), _out()
     lib().oracle_ethash_hashimoto(dag.ctypes.data, dag.size // 128, header_hash, nonce, mix, res)
     return mix.raw, res.raw
+
+
+def ethash_cache(seed: bytes, n_nodes: int) -> np.ndarray:
+    """Light cache of n_nodes 64-byte nodes."""
+    out = np.empty(64 * n_nodes, dtype=np.uint8)
+    lib().oracle_ethash_mkcache(seed, n_nodes, out.ctypes.data)
+    return out
+
+
+def ethash_dataset(cache: np.ndarray, first: int, count: int) -> np.ndarray:
+    """DAG nodes [first, first+count) of 64 bytes each."""
+    out = np.empty(64 * count, dtype=np.uint8)
+    lib().oracle_ethash_dataset(cache.ctypes.data, cache.size // 64, first, count, out.ctypes.data)
+    return out
 
 
 def search(kind: int, header: bytes, start: int, count: int, target: bytes,

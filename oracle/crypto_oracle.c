@@ -373,6 +373,47 @@ EXPORT void oracle_ethash_hashimoto(const uint8_t *dag, uint32_t n_items, const 
 }
 
 /* ------------------------------------------------------------------ */
+/* ethash light cache and DAG generation (public ethash specification, revision 23):
+ *   cache:  o[0] = Keccak-512(seed), o[i] = Keccak-512(o[i-1]); then 3 rounds of
+ *           o[i] = Keccak-512(o[(i-1+n) % n] xor o[o[i][0] % n])
+ *   node i: mix = cache[i % n]; mix[0] ^= i; mix = Keccak-512(mix);
+ *           256 times: mix = fnv(mix, cache[fnv(i ^ j, mix[j % 16]) % n]); node = Keccak-512(mix)
+ * Nodes are 64 bytes; a 128-byte DAG item is two consecutive nodes. */
+EXPORT void oracle_ethash_mkcache(const uint8_t seed[32], uint32_t n, uint8_t *cache) {
+    oracle_keccak(seed, 32, 72, 0x01, cache, 64);
+    for (uint32_t i = 1; i < n; ++i) oracle_keccak(cache + 64 * (size_t)(i - 1), 64, 72, 0x01, cache + 64 * (size_t)i, 64);
+    for (int round = 0; round < 3; ++round)
+        for (uint32_t i = 0; i < n; ++i) {
+            uint32_t v = load_le32(cache + 64 * (size_t)i) % n;
+            uint8_t x[64];
+            const uint8_t *a = cache + 64 * (size_t)((i + n - 1) % n), *b = cache + 64 * (size_t)v;
+            for (int k = 0; k < 64; ++k) x[k] = a[k] ^ b[k];
+            oracle_keccak(x, 64, 72, 0x01, cache + 64 * (size_t)i, 64);
+        }
+}
+
+EXPORT void oracle_ethash_dataset_node(const uint8_t *cache, uint32_t n, uint32_t i, uint8_t out[64]) {
+    uint32_t mix[16];
+    uint8_t buf[64];
+    for (int k = 0; k < 16; ++k) mix[k] = load_le32(cache + 64 * (size_t)(i % n) + 4 * k);
+    mix[0] ^= i;
+    for (int k = 0; k < 16; ++k) store_le32(buf + 4 * k, mix[k]);
+    oracle_keccak(buf, 64, 72, 0x01, buf, 64);
+    for (int k = 0; k < 16; ++k) mix[k] = load_le32(buf + 4 * k);
+    for (uint32_t j = 0; j < 256; ++j) {
+        const uint32_t parent = fnv(i ^ j, mix[j % 16]) % n;
+        for (int k = 0; k < 16; ++k) mix[k] = fnv(mix[k], load_le32(cache + 64 * (size_t)parent + 4 * k));
+    }
+    for (int k = 0; k < 16; ++k) store_le32(buf + 4 * k, mix[k]);
+    oracle_keccak(buf, 64, 72, 0x01, out, 64);
+}
+
+EXPORT void oracle_ethash_dataset(const uint8_t *cache, uint32_t n, uint32_t first, uint32_t count, uint8_t *out) {
+#pragma omp parallel for schedule(static)
+    for (uint32_t k = 0; k < count; ++k) oracle_ethash_dataset_node(cache, n, first + k, out + 64 * (size_t)k);
+}
+
+/* ------------------------------------------------------------------ */
 /* Nonce sweeps (OpenMP over nonces).  Hits come back sorted by nonce.
  * kind: 0 = BLAKE-256, 1 = SHA-256d, 2 = Sia BLAKE2b-256, 3 = ethash.
  * Returns the number of hits found; when that exceeds max_hits only an

@@ -182,3 +182,26 @@ def hashimoto(dag: bytes, n_items: int, header_hash: bytes, nonce: int):
         cmix.append(_fnv(_fnv(_fnv(mix[i], mix[i + 1]), mix[i + 2]), mix[i + 3]))
     mix_digest = struct.pack("<8I", *cmix)
     return mix_digest, keccak256(seed + mix_digest)
+
+
+def ethash_cache(seed: bytes, n: int) -> list:
+    """Light cache as a list of n 64-byte strings (sequential by construction)."""
+    o = [keccak512(seed)]
+    for _ in range(1, n):
+        o.append(keccak512(o[-1]))
+    for _ in range(3):
+        for i in range(n):
+            v = struct.unpack_from("<I", o[i])[0] % n
+            o[i] = keccak512(bytes(a ^ b for a, b in zip(o[(i - 1 + n) % n], o[v])))
+    return o
+
+
+def ethash_dataset_node(cache: list, i: int) -> bytes:
+    n = len(cache)
+    mix = list(struct.unpack("<16I", cache[i % n]))
+    mix[0] ^= i
+    mix = list(struct.unpack("<16I", keccak512(struct.pack("<16I", *mix))))
+    for j in range(256):
+        parent = struct.unpack("<16I", cache[_fnv(i ^ j, mix[j % 16]) % n])
+        mix = [_fnv(a, b) for a, b in zip(mix, parent)]
+    return keccak512(struct.pack("<16I", *mix))

@@ -161,3 +161,18 @@ def test_full_nonce_space_sweep_config3(dev):
     t = crypto.target_from_difficulty_bits(16)
     assert crypto.run(crypto.Blake256(c["blake_header"], 0, 1 << 22, t)).nonces() == \
         OC.search(0, c["blake_header"], 0, 1 << 22, t)[1]
+
+
+def test_dag_generation_matches_oracle_and_feeds_the_search(dev):
+    """Light cache on the host, DAG nodes on the GPU, then a search over the generated DAG."""
+    seed = workloads.xoshiro_bytes(55, 32).tobytes()
+    n_cache, n_nodes = 1021, 2 * 1543                       # odd sizes on purpose
+    cache = crypto.make_cache(seed, n_cache)
+    assert np.array_equal(cache, OC.ethash_cache(seed, n_cache))
+    dag = crypto.generate_dag(torch.from_numpy(cache).to(dev), n_nodes, chunks=3)
+    ref = OC.ethash_dataset(cache, 0, n_nodes)
+    assert np.array_equal(dag.cpu().numpy(), ref)
+    hh = workloads.xoshiro_bytes(56, 32).tobytes()
+    out, mix = crypto.hash_batch("ethash", hh, 1000, 40, dag)
+    for i in range(40):
+        assert (mix[i].tobytes(), out[i].tobytes()) == OC.hashimoto(ref, hh, 1000 + i)

@@ -109,3 +109,17 @@ def test_golden_sweeps_and_target_rule(kat):
     sw = kat["sweeps"]["ethash"]
     found, nonces, mix = OC.search(3, hh, sw["start"], sw["count"], easy, dag=dag)
     assert nonces == sw["nonces"] and [m.hex() for m in mix] == sw["mix"]
+
+
+def test_dag_generation_restatements_agree():
+    seed = bytes(range(32))
+    c = OC.ethash_cache(seed, 67)
+    pc = OP.ethash_cache(seed, 67)
+    assert c.tobytes() == b"".join(pc)
+    d = OC.ethash_dataset(c, 5, 12)
+    for k in range(12):
+        assert d[64 * k:64 * k + 64].tobytes() == OP.ethash_dataset_node(pc, 5 + k)
+    # the library's host-side cache builder is a third implementation of the same chain
+    from hfuse_b200 import crypto
+    import numpy as np
+    assert np.array_equal(crypto.make_cache(seed, 67), c)
