@@ -421,8 +421,8 @@ def run_ours(args):
         b.moments = None
     t_kernel = graph_region(torch, lambda i: ops.run_pair(*sets[i % NSETS]), NSETS, max(args.steps, 120), 3)
 
-    # context for the roofline fraction: a plain device copy that moves the same number of bytes
-    # (half read, half written), timed the same way, same rotation depth
+    # context for the roofline fraction: a device-to-device copy (tensor.copy_, i.e. cudaMemcpyAsync)
+    # that moves the same number of bytes (half read, half written), timed the same way
     half = nbytes // 2 // 4
     csrc = [torch.empty(half, dtype=torch.float32, device=dev).normal_() for _ in range(NSETS)]
     cdst = [torch.empty(half, dtype=torch.float32, device=dev) for _ in range(NSETS)]
@@ -481,7 +481,7 @@ def run_ours(args):
                      "frac": round(nbytes / t_kernel / 1e6 / peak, 4), "traffic": NCU_TRAFFIC_BYTES,
                      "peak_kind": peak_kind, "kernel": "fused_kernel<UpsampleRole,BnStatsRole>",
                      "kernel_us": round(t_kernel * 1e3, 2),
-                     "same_bytes_device_copy_us": round(t_copy * 1e3, 2)},
+                     "same_bytes_memcpy_d2d_us": round(t_copy * 1e3, 2)},
         "clocks": clocks,
     }
     if rank == 0 and world == 1:
