@@ -40,6 +40,16 @@ __device__ __forceinline__ void stg_stream4(float* p, float4 v) {
     asm volatile("st.global.cs.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
                  : "memory");
 }
+// 256-bit stores (sm_100): half as many store instructions for the write-dominated kernels;
+// measured 7 % faster than two 128-bit stores on the x2 upsample.  The address must be 32-byte aligned.
+__device__ __forceinline__ void stg_stream8(float* p, const float* o) {
+    asm volatile("st.global.cs.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(o[0]), "f"(o[1]), "f"(o[2]),
+                 "f"(o[3]), "f"(o[4]), "f"(o[5]), "f"(o[6]), "f"(o[7])
+                 : "memory");
+}
+__device__ __forceinline__ void stg_stream_4xi64(long long* p, long long a, long long b, long long c, long long d) {
+    asm volatile("st.global.cs.v4.s64 [%0], {%1,%2,%3,%4};" ::"l"(p), "l"(a), "l"(b), "l"(c), "l"(d) : "memory");
+}
 __device__ __forceinline__ void stg_stream1(float* p, float v) {
     asm volatile("st.global.cs.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
 }

@@ -22,6 +22,7 @@ namespace {
 constexpr long long kMaxItems = (1LL << 31) - 1;
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
 
 // ------------------------------------------------------------------ argument checking
 int prep_im2col(HFUSE_IM2COL_PARAMS(), Im2colArgs& a) {
@@ -43,7 +44,9 @@ int prep_im2col(HFUSE_IM2COL_PARAMS(), Im2colArgs& a) {
     a.mode = (kh == 3 && kw == 3 && sh == 1 && sw == 1 && dh == 1 && dw == 1 && (Wc % 4) == 0 && items > 0 &&
               items <= kMaxItems)
                  ? 1 : 0;
-    a.div_w4 = make_fastdiv(a.mode == 1 ? (uint32_t)(Wc / 4) : 1u);
+    // tap planes start at multiples of Hc*Wc floats: with Wc % 8 == 0 every row start is 32-byte aligned
+    if (a.mode == 1 && ph == 1 && pw == 1 && (Wc % 8) == 0 && (W % 4) == 0 && aligned32(col)) a.mode = 2;
+    a.div_w4 = make_fastdiv(a.mode == 2 ? (uint32_t)(Wc / 8) : a.mode == 1 ? (uint32_t)(Wc / 4) : 1u);
     a.div_hc = make_fastdiv((uint32_t)Hc);
     return HFUSE_OK;
 }
@@ -65,6 +68,7 @@ int prep_maxpool(HFUSE_MAXPOOL_PARAMS(), MaxPoolArgs& a) {
     a.mode = (kh == 2 && kw == 2 && sh == 2 && sw == 2 && ph == 0 && pw == 0 && dh == 1 && dw == 1 &&
               (pW % 4) == 0 && (W % 4) == 0 && 2LL * pH <= H && 2LL * pW <= W && items <= kMaxItems)
                  ? 1 : 0;
+    a.wide = aligned32(idx) ? 1 : 0;
     a.div_p4 = make_fastdiv(a.mode == 1 ? (uint32_t)(pW / 4) : 1u);
     a.div_ph = make_fastdiv((uint32_t)pH);
     return HFUSE_OK;
@@ -105,6 +109,7 @@ int prep_upsample(HFUSE_UPSAMPLE_PARAMS(), UpsampleArgs& a) {
     a.mode = ((outW % 4) == 0 && items <= kMaxItems) ? 1 : 0;
     const long long strips = (long long)N * C * (H + 1LL) * (W / 4);
     if (!align_corners && outH == 2LL * H && outW == 2LL * W && (W % 4) == 0 && strips <= kMaxItems) a.mode = 2;
+    a.wide = aligned32(out) ? 1 : 0;
     a.div_w4 = make_fastdiv(a.mode == 2 ? (uint32_t)(W / 4) : 1u);
     a.div_j = make_fastdiv((uint32_t)H + 1u);
     return HFUSE_OK;

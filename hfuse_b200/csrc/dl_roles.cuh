@@ -28,8 +28,9 @@ struct Im2colArgs {
     int N, C, H, W;
     int kh, kw, ph, pw, sh, sw, dh, dw;
     int Hc, Wc;
-    int mode;   // 0 = generic (one output element per item), 1 = 3x3 stride-1 tile path
-    FastDiv div_w4, div_hc;   // tile path: by Wc/4 and by Hc
+    int mode;   // 0 = generic (one output element per item), 1 = 3x3 stride-1 tile path (4 columns per item),
+                // 2 = the same with 8 columns per item and 256-bit stores (pad 1, Wc % 8 == 0, col 32-byte aligned)
+    FastDiv div_w4, div_hc;   // tile paths: by Wc/4 (mode 1) or Wc/8 (mode 2), and by Hc
 };
 
 struct Im2colRole {
@@ -104,6 +105,50 @@ struct Im2colRole {
         }
     }
 
+    // 3x3 / stride 1 / pad 1, Wc % 8 == 0: eight adjacent output columns per item, two aligned
+    // 16-byte loads per input row, outer columns from the neighbouring lanes, nine 32-byte stores.
+    template <int T>
+    static __device__ __forceinline__ void run_k3s1_wide(const Args& a, const RoleCtx& ctx) {
+        const unsigned W8 = (unsigned)a.Wc >> 3;
+        const unsigned total = (unsigned)a.N * a.C * a.Hc * W8;     // host guarantees < 2^31
+        const size_t tap_stride = (size_t)a.Hc * a.Wc;
+        const unsigned lane = ctx.tid & 31;
+        for (unsigned base = (unsigned)ctx.block * T + (ctx.tid & ~31); base < total;
+             base += (unsigned)ctx.nblocks * T) {
+            const bool live = base + lane < total;
+            const unsigned it = live ? base + lane : total - 1;
+            unsigned w8, h;
+            const unsigned r = fast_divmod(it, a.div_w4, w8);
+            const unsigned plane = fast_divmod(r, a.div_hc, h);
+            const float* src = a.im + (size_t)plane * a.H * a.W;
+            float* dst = a.col + (size_t)plane * 9 * tap_stride + h * a.Wc + w8 * 8;
+            const bool has_l = w8 > 0, has_r = w8 + 1 < W8;
+            float v[3][10];
+#pragma unroll
+            for (int i = 0; i < 3; ++i) {
+                const int hi = (int)h - 1 + i;
+                const bool row_ok = (hi >= 0) && (hi < a.H);
+                const float* row = src + (size_t)(row_ok ? hi : 0) * a.W + w8 * 8;
+                const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 m0 = row_ok ? __ldg(reinterpret_cast<const float4*>(row)) : z;
+                const float4 m1 = row_ok ? __ldg(reinterpret_cast<const float4*>(row + 4)) : z;
+                float left = __shfl_up_sync(0xffffffffu, m1.w, 1);
+                float right = __shfl_down_sync(0xffffffffu, m0.x, 1);
+                if (lane == 0 && has_l) left = row_ok ? __ldg(row - 1) : 0.f;
+                if (lane == 31 && has_r) right = row_ok ? __ldg(row + 8) : 0.f;
+                v[i][0] = has_l ? left : 0.f;
+                v[i][1] = m0.x; v[i][2] = m0.y; v[i][3] = m0.z; v[i][4] = m0.w;
+                v[i][5] = m1.x; v[i][6] = m1.y; v[i][7] = m1.z; v[i][8] = m1.w;
+                v[i][9] = has_r ? right : 0.f;
+            }
+            if (!live) continue;
+#pragma unroll
+            for (int i = 0; i < 3; ++i)
+#pragma unroll
+                for (int j = 0; j < 3; ++j) stg_stream8(dst + (size_t)(i * 3 + j) * tap_stride, &v[i][j]);
+        }
+    }
+
     template <int T>
     static __device__ __forceinline__ void run_generic(const Args& a, const RoleCtx& ctx) {
         const unsigned long long plane_out = (unsigned long long)a.Hc * a.Wc;
@@ -129,7 +174,8 @@ struct Im2colRole {
 
     template <int T, int BAR>
     static __device__ __forceinline__ void run(const Args& a, const RoleCtx& ctx) {
-        if (a.mode == 1) run_k3s1<T>(a, ctx);
+        if (a.mode == 2) run_k3s1_wide<T>(a, ctx);
+        else if (a.mode == 1) run_k3s1<T>(a, ctx);
         else run_generic<T>(a, ctx);
     }
 };
@@ -145,6 +191,7 @@ struct MaxPoolArgs {
     int kh, kw, sh, sw, ph, pw, dh, dw;
     int mode;   // 0 = generic, 1 = 2x2 stride 2 without padding, pW % 4 == 0, W % 4 == 0
     FastDiv div_p4, div_ph;   // 2x2 path: by pW/4 and by pH
+    int wide;                 // idx is 32-byte aligned: one 256-bit store for the four indices
 };
 
 __device__ __forceinline__ void pool_take(float v, int at, float& best, int& best_at) {
@@ -187,8 +234,8 @@ struct MaxPoolRole {
             }
             const size_t o_off = ((size_t)plane * pH + oh) * a.pW + 4 * p4;
             stg_stream4(a.out + o_off, make_float4(best[0], best[1], best[2], best[3]));
-            stg_stream_2xi64(a.idx + o_off, at[0], at[1]);
-            stg_stream_2xi64(a.idx + o_off + 2, at[2], at[3]);
+            if (a.wide) stg_stream_4xi64(a.idx + o_off, at[0], at[1], at[2], at[3]);
+            else { stg_stream_2xi64(a.idx + o_off, at[0], at[1]); stg_stream_2xi64(a.idx + o_off + 2, at[2], at[3]); }
         }
     }
 
@@ -236,6 +283,7 @@ struct UpsampleArgs {
     int mode;   // 0 = one output per item, 1 = four adjacent outputs per item (outW % 4 == 0),
                 // 2 = exact x2 strip path (run_x2)
     FastDiv div_w4, div_j;   // x2 path: by W/4 and by H+1
+    int wide;                // output is 32-byte aligned: 256-bit stores
 };
 
 __device__ __forceinline__ void bilinear_src(float scale, int dst, int align, int in_size, int& i1, int& i1p,
@@ -359,8 +407,8 @@ struct UpsampleRole {
 #pragma unroll
                 for (int k = 0; k < 8; ++k) o[k] = __fadd_rn(__fmul_rn(0.75f, ta[k]), __fmul_rn(0.25f, tb[k]));
                 float* p = orow + (size_t)(2 * j - 1) * a.outW;
-                stg_stream4(p, make_float4(o[0], o[1], o[2], o[3]));
-                stg_stream4(p + 4, make_float4(o[4], o[5], o[6], o[7]));
+                if (a.wide) stg_stream8(p, o);
+                else { stg_stream4(p, make_float4(o[0], o[1], o[2], o[3])); stg_stream4(p + 4, make_float4(o[4], o[5], o[6], o[7])); }
             }
             if (j < a.H) {      // even output row 2j: weights (0.25, 0.75), or (1, 0) on the clamped row 0
                 const float h0 = j == 0 ? 1.f : 0.25f, h1 = j == 0 ? 0.f : 0.75f;
@@ -368,8 +416,8 @@ struct UpsampleRole {
 #pragma unroll
                 for (int k = 0; k < 8; ++k) o[k] = __fadd_rn(__fmul_rn(h0, ta[k]), __fmul_rn(h1, tb[k]));
                 float* p = orow + (size_t)(2 * j) * a.outW;
-                stg_stream4(p, make_float4(o[0], o[1], o[2], o[3]));
-                stg_stream4(p + 4, make_float4(o[4], o[5], o[6], o[7]));
+                if (a.wide) stg_stream8(p, o);
+                else { stg_stream4(p, make_float4(o[0], o[1], o[2], o[3])); stg_stream4(p + 4, make_float4(o[4], o[5], o[6], o[7])); }
             }
         }
     }

@@ -205,3 +205,32 @@ def test_error_codes_on_device_buffers(dev):
     assert e.value.code == -4
     with pytest.raises(ValueError):
         ops.Histc(x, 4, 2.0, 1.0)
+
+
+def _offset16(shape, dtype, dev):
+    """A tensor whose storage starts 16 bytes past a 32-byte boundary (allowed by the ABI)."""
+    n = int(np.prod(shape))
+    step = 16 // torch.empty(0, dtype=dtype).element_size()
+    base = torch.empty(n + 2 * step, dtype=dtype, device=dev)
+    off = step if base.data_ptr() % 32 == 0 else 0
+    t = base[off:off + n].view(*shape)
+    assert t.data_ptr() % 32 == 16
+    return t
+
+
+def test_outputs_that_are_only_16_byte_aligned_take_the_narrow_store_paths(dev):
+    g = torch.Generator().manual_seed(18)
+    x = torch.rand(2, 3, 8, 16, generator=g) * 2 - 1
+    col = _offset16((2, 27, 128), torch.float32, dev)
+    ops.run(ops.Im2col(x.to(dev), 3, 1, 1, 1, out=col))
+    assert torch.equal(col.cpu(), dl.im2col_torch(x, 3, 3, 1, 1, 1, 1, 1, 1))
+    up = _offset16((2, 3, 16, 32), torch.float32, dev)
+    u = torch.rand(2, 3, 8, 16, generator=g)
+    ops.run(ops.Upsample(u.to(dev), scale_factor=2, out=up))
+    assert np.array_equal(up.cpu().numpy(), dl.upsample_numpy(u.numpy(), 16, 32))
+    idx = _offset16((2, 3, 4, 8), torch.int64, dev)
+    p = torch.randint(0, 3, (2, 3, 8, 16), generator=g).float()
+    op = ops.MaxPool(p.to(dev), 2, 2, indices=idx)
+    ops.run(op)
+    vr, ir = dl.maxpool_torch(p, 2, 2, 2, 2, 0, 0, 1, 1)
+    assert torch.equal(op.out.cpu(), vr) and torch.equal(idx.cpu(), ir)
