@@ -432,37 +432,69 @@ def run_ours(args):
     # ---- end to end through the C ABI with host buffers (pinned), copies inside the timed region
     w = workloads.config1()
     h_up, h_bn = w["up"].pin_memory(), w["bn"].pin_memory()
-    a0, b0 = sets[0]
-    h_out = torch.empty(a0.out.shape, dtype=torch.float32).pin_memory()
-    h_stats = torch.empty((2, 256), dtype=torch.float32).pin_memory()
-    e2e_steps = max(3, min(args.steps, 10))
+    # Two buffer sets and three streams (upload, kernel, download): the upload of step i+1 and
+    # the download of step i-1 overlap the kernel of step i, so both PCIe directions are busy at
+    # once.  Every step still uploads its own inputs and downloads its own outputs; the host
+    # takes the results of a step as soon as its download event has completed.
+    DEPTH = 2
+    h_outs = [torch.empty(sets[0][0].out.shape, dtype=torch.float32).pin_memory() for _ in range(DEPTH)]
+    h_stats = [torch.empty((2, 256), dtype=torch.float32).pin_memory() for _ in range(DEPTH)]
+    s_in, s_k, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    uploaded = [None] * DEPTH
+    computed = [None] * DEPTH
+    downloaded = [None] * DEPTH
+    e2e_steps = max(4, min(args.steps, 12))
 
     def e2e_step(i):
-        a0.x.copy_(h_up, non_blocking=True)
-        b0.x.copy_(h_bn, non_blocking=True)
-        ops.run_pair(a0, b0)
-        h_out.copy_(a0.out, non_blocking=True)
-        h_stats[0].copy_(b0.mean, non_blocking=True)
-        h_stats[1].copy_(b0.invstd, non_blocking=True)
-        torch.cuda.current_stream().synchronize()        # the caller holds its result
-    for i in range(2):
+        k = i % DEPTH
+        a0, b0 = sets[k]
+        with torch.cuda.stream(s_in):
+            if computed[k] is not None:
+                s_in.wait_event(computed[k])           # the previous kernel on this set has read its inputs
+            a0.x.copy_(h_up, non_blocking=True)
+            b0.x.copy_(h_bn, non_blocking=True)
+            uploaded[k] = torch.cuda.Event()
+            uploaded[k].record()
+        with torch.cuda.stream(s_k):
+            s_k.wait_event(uploaded[k])
+            if downloaded[k] is not None:
+                s_k.wait_event(downloaded[k])          # the previous outputs of this set have left the device
+            ops.run_pair(a0, b0)
+            computed[k] = torch.cuda.Event()
+            computed[k].record()
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(computed[k])
+            if downloaded[k] is not None:
+                downloaded[k].synchronize()            # the host has finished with this pinned buffer
+            h_outs[k].copy_(a0.out, non_blocking=True)
+            h_stats[k][0].copy_(b0.mean, non_blocking=True)
+            h_stats[k][1].copy_(b0.invstd, non_blocking=True)
+            downloaded[k] = torch.cuda.Event()
+            downloaded[k].record()
+
+    def e2e_drain():
+        for ev in downloaded:
+            if ev is not None:
+                ev.synchronize()                       # the caller holds every result
+    for i in range(DEPTH):
         e2e_step(i)
+    e2e_drain()
+    torch.cuda.synchronize()
     barrier()
     t0 = time.perf_counter()
-    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s2.record()
     for i in range(e2e_steps):
         e2e_step(i)
-    e2.record()
-    torch.cuda.synchronize()
-    e2e_ms = max(s2.elapsed_time(e2), (time.perf_counter() - t0) * 1e3) / e2e_steps
+    e2e_drain()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps      # host clock: it ends when the results are on the host
+    a0, b0 = sets[0]
+    h_out = h_outs[0]
     if use_dist:
         import torch.distributed as dist
         t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     h2d = h_up.numel() * 4 + h_bn.numel() * 4
-    d2h = h_out.numel() * 4 + h_stats.numel() * 4
+    d2h = h_out.numel() * 4 + h_stats[0].numel() * 4
 
     line = {
         "metric": "fused upsample_bilinear2d + batch_norm_collect_statistics pair, HBM throughput",
@@ -476,7 +508,8 @@ def run_ours(args):
                    "parallelism": f"batch-sharded x{world}", "collective": collective},
         "gpu_launches": launches,
         "e2e": {"value": round(world * nbytes / e2e_ms / 1e6, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 4)},
+                "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 4),
+                "pipeline": "2 buffer sets, upload / kernel / download streams overlapped"},
         "roofline": {"bound": "hbm", "achieved": round(nbytes / t_kernel / 1e6, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(nbytes / t_kernel / 1e6 / peak, 4), "traffic": NCU_TRAFFIC_BYTES,
                      "peak_kind": peak_kind, "kernel": "fused_kernel<UpsampleRole,BnStatsRole>",
