@@ -77,7 +77,7 @@ int prep_common(uint64_t start, uint64_t count, const uint8_t* target32, hfuse_h
     if (!target32 || !hits) return HFUSE_ERR_BAD_ARG;
     if (nonce32 && count > (1ull << 32)) return HFUSE_ERR_TOO_LARGE;   // the nonce space itself
     if (count > (1ull << 62)) return HFUSE_ERR_TOO_LARGE;
-    c.start = start; c.count = count; c.hits = hits; c.out32 = nullptr; c.mix32 = nullptr;
+    c.start = start; c.count = count; c.hits = hits; c.out32 = nullptr; c.mix32 = nullptr; c.one = 1u;
     for (int i = 0; i < 8; ++i) c.target[i] = be32(target32 + 4 * i);
     return HFUSE_OK;
 }
