@@ -58,7 +58,7 @@ def measured_peak_gbs():
 
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,utilization.gpu,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -87,13 +87,15 @@ class ClockSampler:
             self.proc.kill()
         try:
             rows = [r.strip().split(", ") for r in open(self.path) if r.strip()]
-            sm = [float(r[1]) for r in rows if len(r) >= 9]
-            if sm:
-                out["sm_mhz"] = statistics.median(sm)
-                out["sm_max_mhz"] = float(rows[0][2])
+            rows = [r for r in rows if len(r) >= 10]
+            busy = [r for r in rows if r[4].strip().isdigit() and int(r[4]) >= 50] or rows   # samples under load
+            if busy:
+                out["sm_mhz"] = statistics.median(float(r[1]) for r in busy)
+                out["sm_max_mhz"] = float(busy[0][2])
                 names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-                out["reasons"] = [n for k, n in enumerate(names) if any(r[5 + k].startswith("Active") for r in rows)]
-                out["samples"] = len(sm)
+                out["reasons"] = [n for k, n in enumerate(names) if any(r[6 + k].startswith("Active") for r in busy)]
+                out["samples"] = len(busy)
+                out["power_w_max"] = max(float(r[3]) for r in busy)
         except Exception:
             pass
         finally:
@@ -407,7 +409,6 @@ def run_ours(args):
     torch.cuda.synchronize()
     barrier()
     ms = s.elapsed_time(e)
-    clocks = sampler.stop()
     launches = per_step_launches * args.steps
     if use_dist:
         import torch.distributed as dist
@@ -420,6 +421,15 @@ def run_ours(args):
     for (a, b) in sets:
         b.moments = None
     t_kernel = graph_region(torch, lambda i: ops.run_pair(*sets[i % NSETS]), NSETS, max(args.steps, 120), 3)
+    # The timed region lasts a few milliseconds, shorter than one nvidia-smi sampling period, so the
+    # sampler stays on while the same kernel keeps running (this measurement, then up to a second
+    # more of the same launches) until it has seen the GPU under load a few times.
+    t_end = time.perf_counter() + 1.0
+    while time.perf_counter() < t_end:
+        for i in range(NSETS * 40):
+            ops.run_pair(*sets[i % NSETS])
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
 
     # context for the roofline fraction: a device-to-device copy (tensor.copy_, i.e. cudaMemcpyAsync)
     # that moves the same number of bytes (half read, half written), timed the same way
