@@ -64,6 +64,7 @@ def exported_symbols() -> list[str]:
               "hfuse_exchange_status", "hfuse_exchange_destroy", "hfuse_bnstats_allreduce_f32",
               "hfuse_upsample_bnstats_allreduce_f32"]
     names += ["hfuse_ethash_make_cache", "hfuse_ethash_generate_dag"]
+    names += ["hfuse_maxpool2d_backward_f32", "hfuse_bn_backward_f32", "hfuse_maxpool_backward_bn_backward_f32"]
     names += ["hfuse_error_string", "hfuse_version", "hfuse_bnstats_workspace_bytes", "hfuse_bnstats_noalloc_f32",
               "hfuse_bnstats_finalize_f64", "hfuse_hits_reset", "hfuse_hash_batch", "hfuse_tune_set",
               "hfuse_tune_describe", "hfuse_xoshiro256ss_fill"]
@@ -115,6 +116,12 @@ def lib() -> C.CDLL:
     L.hfuse_bnstats_allreduce_f32.restype, L.hfuse_bnstats_allreduce_f32.argtypes = _i, BNSTATS + [_p, _p]
     L.hfuse_upsample_bnstats_allreduce_f32.restype = _i
     L.hfuse_upsample_bnstats_allreduce_f32.argtypes = UPSAMPLE + BNSTATS + [_p, _p]
+    MPB = [_p, _p] + [_i] * 14 + [_p]
+    BNB = [_p, _p, _i, _i, _i, _p, _p, _p, _p, _p, _p]
+    L.hfuse_maxpool2d_backward_f32.restype, L.hfuse_maxpool2d_backward_f32.argtypes = _i, MPB + [_p]
+    L.hfuse_bn_backward_f32.restype, L.hfuse_bn_backward_f32.argtypes = _i, BNB + [_p]
+    L.hfuse_maxpool_backward_bn_backward_f32.restype = _i
+    L.hfuse_maxpool_backward_bn_backward_f32.argtypes = MPB + BNB + [_p]
     L.hfuse_ethash_make_cache.restype, L.hfuse_ethash_make_cache.argtypes = _i, [C.c_char_p, _u32, _p]
     L.hfuse_ethash_generate_dag.restype = _i
     L.hfuse_ethash_generate_dag.argtypes = [_p, _u32, _p, _u32, _u32, _p]

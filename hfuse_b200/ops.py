@@ -254,3 +254,60 @@ def bn_finalize(moments: torch.Tensor, eps: float):
                                                      invstd.data_ptr(), _stream_ptr()),
                "hfuse_bnstats_finalize_f64")
     return mean, invstd
+
+
+# ---- backward kernels (listed by the reference next to the forward ones, never fused there) ------
+class MaxPoolBackward:
+    """grad_in of max_pool2d from grad_out and the indices a MaxPool operator wrote."""
+
+    def __init__(self, fwd: MaxPool, grad_out: torch.Tensor):
+        self.fwd = fwd
+        self.grad_out = _check_input(grad_out, "max_pool grad_out")
+        if tuple(grad_out.shape) != tuple(fwd.out.shape):
+            raise ValueError("grad_out must have the shape of the pooled output")
+        self.grad_in = torch.empty_like(fwd.x)
+
+    def c_args(self):
+        f = self.fwd
+        N, C, H, W = f.x.shape
+        return [self.grad_out.data_ptr(), f.idx.data_ptr(), N, C, H, W, f.pH, f.pW, f.kh, f.kw, f.sh, f.sw, f.ph, f.pw,
+                f.dh, f.dw, self.grad_in.data_ptr()]
+
+
+class BnBackward:
+    """Training-mode batch-norm backward from the saved mean / invstd of the statistics kernel."""
+
+    def __init__(self, x, grad_out, mean, invstd, weight=None):
+        self.x, self.dy = _check_input(x, "batch_norm input"), _check_input(grad_out, "batch_norm grad_out")
+        if x.shape != grad_out.shape:
+            raise ValueError("grad_out must have the shape of the input")
+        self.N, self.C = x.shape[0], x.shape[1]
+        self.HW = x.numel() // (self.N * self.C)
+        self.mean, self.invstd, self.weight = mean, invstd, weight
+        self.dx = torch.empty_like(x)
+        self.grad_weight = torch.empty(self.C, dtype=torch.float32, device=x.device)
+        self.grad_bias = torch.empty(self.C, dtype=torch.float32, device=x.device)
+
+    def c_args(self):
+        return [self.x.data_ptr(), self.dy.data_ptr(), self.N, self.C, self.HW,
+                self.weight.data_ptr() if self.weight is not None else None, self.mean.data_ptr(),
+                self.invstd.data_ptr(), self.dx.data_ptr(), self.grad_weight.data_ptr(), self.grad_bias.data_ptr()]
+
+
+def max_pool2d_backward(fwd: MaxPool, grad_out, stream=None):
+    op = MaxPoolBackward(fwd, grad_out)
+    _lib.check(_lib.lib().hfuse_maxpool2d_backward_f32(*op.c_args(), _stream_ptr(stream)), "hfuse_maxpool2d_backward_f32")
+    return op.grad_in
+
+
+def batch_norm_backward(x, grad_out, mean, invstd, weight=None, stream=None):
+    op = BnBackward(x, grad_out, mean, invstd, weight)
+    _lib.check(_lib.lib().hfuse_bn_backward_f32(*op.c_args(), _stream_ptr(stream)), "hfuse_bn_backward_f32")
+    return op.dx, op.grad_weight, op.grad_bias
+
+
+def run_backward_pair(mp: MaxPoolBackward, bn: BnBackward, stream=None):
+    """max-pool backward and batch-norm backward in ONE fused launch."""
+    _lib.check(_lib.lib().hfuse_maxpool_backward_bn_backward_f32(*mp.c_args(), *bn.c_args(), _stream_ptr(stream)),
+               "hfuse_maxpool_backward_bn_backward_f32")
+    return mp.grad_in, (bn.dx, bn.grad_weight, bn.grad_bias)

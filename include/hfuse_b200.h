@@ -158,6 +158,30 @@ HFUSE_API int hfuse_histc_bnstats_f32(HFUSE_HISTC_PARAMS(a_), HFUSE_BNSTATS_PARA
                                       hfuse_stream_t stream);                         /* ml_fusion.yaml:37-40 */
 
 /* ---------------------------------------------------------------------------------------
+ * Backward kernels.  The reference lists them beside the forward kernels but fuses none of
+ * them (configs/ml_kernels.yaml:46-63: max_pool_backward_nchw, and batch_norm_backward_kernel,
+ * its only kernel with HasBarriers: true).
+ *   max-pool: grad_in[n,c,h,w] = sum of grad_out over the outputs whose index is h*W+w
+ *             (idx as written by hfuse_maxpool2d_f32).
+ *   batch-norm (training mode, saved mean / invstd from the statistics kernel; weight may be
+ *             NULL = 1; grad_in / grad_weight / grad_bias may each be NULL):
+ *             grad_bias = sum(dy), grad_weight = sum(dy (x-mean)) invstd,
+ *             grad_in = (dy - sum(dy)/M - (x-mean) invstd^2 sum(dy (x-mean))/M) invstd weight.
+ * The pair runs both in one block (max-pool range | batch-norm range with its named barrier).
+ * ------------------------------------------------------------------------------------- */
+HFUSE_API int hfuse_maxpool2d_backward_f32(const float* grad_out, const int64_t* idx, int N, int C, int H, int W,
+                                           int pH, int pW, int kh, int kw, int sh, int sw, int ph, int pw, int dh,
+                                           int dw, float* grad_in, hfuse_stream_t stream);
+HFUSE_API int hfuse_bn_backward_f32(const float* x, const float* grad_out, int N, int C, int HW, const float* weight,
+                                    const float* mean, const float* invstd, float* grad_in, float* grad_weight,
+                                    float* grad_bias, hfuse_stream_t stream);
+HFUSE_API int hfuse_maxpool_backward_bn_backward_f32(
+    const float* p_grad_out, const int64_t* p_idx, int pN, int pC, int pHin, int pWin, int pH, int pW, int kh, int kw,
+    int sh, int sw, int ph, int pw, int dh, int dw, float* p_grad_in, const float* x, const float* grad_out, int N, int C,
+    int HW, const float* weight, const float* mean, const float* invstd, float* grad_in, float* grad_weight,
+    float* grad_bias, hfuse_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
  * Multi-GPU batch-norm statistics with the cross-GPU sum inside the kernel (no counterpart
  * in the reference, which is single-GPU).  One process per GPU; each creates an exchange
  * object (a small device buffer), publishes its IPC handle, collects every rank's handle

@@ -163,3 +163,18 @@ def histc_numpy(x: np.ndarray, nbins, lo, hi) -> np.ndarray:
         b = (((v - lo32) * np.float32(nbins)) / (hi32 - lo32)).astype(np.int32)
     b = np.where(b == nbins, nbins - 1, b)
     return np.bincount(b, minlength=nbins).astype(np.uint32)
+
+
+# ------------------------------------------------------------------ backward kernels
+def maxpool_backward_torch(x: torch.Tensor, grad_out: torch.Tensor, idx: torch.Tensor, kh, kw, sh, sw, ph, pw, dh, dw):
+    return torch.ops.aten.max_pool2d_with_indices_backward(grad_out, x, [kh, kw], [sh, sw], [ph, pw], [dh, dw], False, idx)
+
+
+def bn_backward_f64(x: torch.Tensor, grad_out: torch.Tensor, weight, eps: float):
+    """Training-mode batch-norm backward in float64: (grad_in, grad_weight, grad_bias)."""
+    xd, gd = x.double(), grad_out.double()
+    dims = [0] + list(range(2, x.dim()))
+    mean = xd.mean(dims)
+    invstd = 1.0 / torch.sqrt(xd.var(dims, unbiased=False) + eps)
+    wd = weight.double() if weight is not None else None
+    return torch.ops.aten.native_batch_norm_backward(gd, xd, wd, None, None, mean, invstd, True, eps, [True, True, True])
