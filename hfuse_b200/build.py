@@ -106,7 +106,28 @@ def build_torch_ext(force: bool = False) -> str:
     return TORCH_EXT
 
 
+FUSER = os.path.join(HERE, "fuser")
+
+
+def build_fuser(force: bool = False) -> str:
+    """The C++ host program over the C ABI (csrc/fuser_main.cpp), the counterpart of the
+    reference's `fuser` binary.  Host-only code: g++ plus the CUDA runtime."""
+    src = os.path.join(CSRC, "fuser_main.cpp")
+    if not force and os.path.exists(FUSER) and os.path.getmtime(FUSER) >= os.path.getmtime(src):
+        return FUSER
+    build()
+    cuda = os.path.dirname(os.path.dirname(_nvcc()))
+    cmd = ["/usr/bin/g++", "-O2", "-std=c++17", src, "-o", FUSER, f"-I{cuda}/include", f"-L{HERE}", "-lhfuse_b200",
+           f"-L{cuda}/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{cuda}/lib64"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"fuser build failed:\n{r.stdout}\n{r.stderr[-4000:]}")
+    return FUSER
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
     if "--torch-ext" in sys.argv:
         print(build_torch_ext(force="--force" in sys.argv))
+    if "--fuser" in sys.argv:
+        print(build_fuser(force="--force" in sys.argv))

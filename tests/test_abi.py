@@ -83,3 +83,14 @@ def test_torch_extension_registers_every_pair_and_refuses_cpu_tensors():
         assert hasattr(torch.ops.hfuse_b200, name), name
     with pytest.raises(RuntimeError, match="no CPU path"):
         torch.ops.hfuse_b200.histc(torch.zeros(4), 4, 0.0, 1.0)
+
+
+def test_public_header_is_valid_c_and_cpp(tmp_path):
+    import subprocess
+    hdr = os.path.join(ROOT, "include", "hfuse_b200.h")
+    for lang, std in (("c", "-std=c99"), ("c++", "-std=c++17")):
+        src = tmp_path / ("t." + ("c" if lang == "c" else "cpp"))
+        src.write_text(f'#include "{hdr}"\nint main(void) {{ return (int)sizeof(hfuse_hits) == 0; }}\n')
+        r = subprocess.run(["/usr/bin/gcc" if lang == "c" else "/usr/bin/g++", std, "-Wall", "-Werror", "-fsyntax-only",
+                            str(src)], capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
