@@ -141,6 +141,10 @@ constexpr int kCryptoSoloVariants = 9;
 template <class RA, class RB>
 int dispatch_pair(const char* name, int default_variant, typename RA::Args a, typename RB::Args b, cudaStream_t s) {
     const Tune t = tune_get(name);
+    // the work-queue cursors must start at zero whatever the caller left in the records
+    if (cudaMemsetAsync(&a.c.hits->reserved, 0, sizeof(uint32_t), s) != cudaSuccess ||
+        cudaMemsetAsync(&b.c.hits->reserved, 0, sizeof(uint32_t), s) != cudaSuccess)
+        return HFUSE_ERR_LAUNCH;
     switch (t.variant >= 0 ? t.variant : default_variant) {
 #define X(I, TA, TB, MB) \
     case I: return launch_pair_queue<RA, RB, TA, TB, MB>(a, b, t.blocks_per_sm, s);

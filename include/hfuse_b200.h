@@ -234,8 +234,8 @@ HFUSE_API int hfuse_upsample_bnstats_allreduce_f32(HFUSE_UPSAMPLE_PARAMS(a_), HF
  * absent ethminer sources).  Device memory; reset it before every search (hfuse_hits_reset):
  * `count` must start at zero and counts every hit found even beyond HFUSE_MAX_HITS; slots
  * are filled in arrival order, so sort by nonce before comparing.  `reserved` is the work
- * queue cursor of the fused searches (thread ranges take chunks of nonces from it) and
- * must also start at zero. */
+ * queue cursor of the fused searches (thread ranges take chunks of nonces from it); the
+ * fused entry points clear it themselves. */
 typedef struct hfuse_hits {
     uint32_t count;
     uint32_t reserved;

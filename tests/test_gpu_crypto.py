@@ -176,3 +176,16 @@ def test_dag_generation_matches_oracle_and_feeds_the_search(dev):
     out, mix = crypto.hash_batch("ethash", hh, 1000, 40, dag)
     for i in range(40):
         assert (mix[i].tobytes(), out[i].tobytes()) == OC.hashimoto(ref, hh, 1000 + i)
+
+
+def test_fused_search_without_a_reset_still_sweeps_everything(dev, kat):
+    """The fused kernels clear their own work-queue cursors: a second launch on records that were
+    not reset finds every hit again (the counts simply keep adding up)."""
+    hdr = bytes.fromhex(kat["header80"])
+    easy = bytes.fromhex(kat["easy_target"])
+    a, b = crypto.Blake256(hdr, 0, 1 << 15, easy), crypto.Sha256d(hdr, 0, 1 << 15, easy)
+    crypto.run_pair(a, b)
+    first = (a.result()[0], b.result()[0])
+    assert first[0] > 0 and first[1] > 0
+    crypto.run_pair(a, b, reset=False)
+    assert (a.result()[0], b.result()[0]) == (2 * first[0], 2 * first[1])
