@@ -315,10 +315,22 @@ def run_ours(args):
     launches = 0
     done = [None] * NSETS
     collective = "none"
+    ex = None
     if use_dist and args.collective == "fused":
-        # the cross-GPU sum of the moments happens inside the fused kernel, over peer memory
+        # the cross-GPU sum of the moments happens inside the fused kernel, over peer memory;
+        # if any rank cannot map its peers' buffers (CUDA IPC refused), every rank falls back to NCCL
+        import torch.distributed as dist
         from hfuse_b200.exchange import BnExchange
-        ex = BnExchange(256)
+        try:
+            ex = BnExchange(256)
+            ok_flag = torch.ones(1, device=dev)
+        except Exception as exc:
+            sys.stderr.write(f"rank {rank}: peer-memory exchange unavailable ({exc!r}); using NCCL\n")
+            ok_flag = torch.zeros(1, device=dev)
+        dist.all_reduce(ok_flag, op=dist.ReduceOp.MIN)
+        if ok_flag.item() == 0:
+            ex = None
+    if ex is not None:
         collective = "in-kernel sum of the [256,3] f64 moments over NVLink peer stores"
 
         def step(i):

@@ -26,15 +26,28 @@ class BnExchange:
         self.channels = int(channels)
         L = _lib.lib()
         self._h = C.c_void_p()
-        _lib.check(L.hfuse_exchange_create(self.world, self.rank, self.channels, C.byref(self._h)),
-                   "hfuse_exchange_create")
+        # Every rank walks through the same collectives even when a local step failed, and all
+        # ranks raise together: nobody is left waiting inside a gather.
+        rc = L.hfuse_exchange_create(self.world, self.rank, self.channels, C.byref(self._h))
         if self.world > 1:
             buf = C.create_string_buffer(64)
-            _lib.check(L.hfuse_exchange_local_handle(self._h, buf), "hfuse_exchange_local_handle")
-            handles = [None] * self.world
-            dist.all_gather_object(handles, buf.raw, group=group)
-            _lib.check(L.hfuse_exchange_connect(self._h, b"".join(handles)), "hfuse_exchange_connect")
-            dist.barrier(group=group)      # every rank has mapped every buffer before the first kernel
+            if rc == 0:
+                rc = L.hfuse_exchange_local_handle(self._h, buf)
+            gathered = [None] * self.world
+            dist.all_gather_object(gathered, (rc, buf.raw), group=group)
+            if all(g[0] == 0 for g in gathered):
+                rc = L.hfuse_exchange_connect(self._h, b"".join(g[1] for g in gathered))
+            else:
+                rc = rc or -5          # a peer failed (HFUSE_ERR_LAUNCH)
+            # doubles as the barrier that says "every rank has mapped every buffer"
+            status = [None] * self.world
+            dist.all_gather_object(status, rc, group=group)
+            bad = [(r, c) for r, c in enumerate(status) if c != 0]
+            if bad:
+                self.close()
+                raise _lib.HfuseError(bad[0][1], f"peer-memory exchange set-up failed on rank {bad[0][0]}")
+        else:
+            _lib.check(rc, "hfuse_exchange_create")
 
     def run(self, bn, stream=None):
         """Standalone statistics kernel with the in-kernel all-reduce."""
@@ -56,7 +69,8 @@ class BnExchange:
 
     def close(self):
         if self._h:
-            torch.cuda.synchronize()
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
             _lib.lib().hfuse_exchange_destroy(self._h)
             self._h = C.c_void_p()
 

@@ -81,3 +81,34 @@ def test_reductions_over_gloo_world_2():
         p.join(120)
         assert p.exitcode == 0
     assert ret[0] and ret[1]
+
+
+def _exchange_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from hfuse_b200 import _lib
+        from hfuse_b200.exchange import BnExchange
+        try:
+            BnExchange(8)
+            ret[rank] = "no error"
+        except _lib.HfuseError as e:
+            ret[rank] = f"raised {e.code}"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="exercises the set-up failure path of a box without a GPU")
+def test_exchange_setup_fails_on_all_ranks_together_without_hanging():
+    """Without a GPU the exchange buffer cannot be created; both ranks must learn that and raise,
+    instead of one of them waiting inside a gather for a peer that gave up."""
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = 31500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_exchange_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert ret[0].startswith("raised") and ret[1].startswith("raised")
