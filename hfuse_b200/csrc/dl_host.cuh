@@ -48,6 +48,10 @@ int prep_im2col(HFUSE_IM2COL_PARAMS(), Im2colArgs& a) {
     if (a.mode == 1 && ph == 1 && pw == 1 && (Wc % 8) == 0 && (W % 4) == 0 && aligned32(col)) a.mode = 2;
     a.div_w4 = make_fastdiv(a.mode == 2 ? (uint32_t)(Wc / 8) : a.mode == 1 ? (uint32_t)(Wc / 4) : 1u);
     a.div_hc = make_fastdiv((uint32_t)Hc);
+    a.div_wc = make_fastdiv((uint32_t)Wc);
+    a.div_taps = make_fastdiv((uint32_t)(kh * kw));
+    a.div_kw = make_fastdiv((uint32_t)kw);
+    a.small = ((long long)N * C * kh * kw * Hc * Wc <= kMaxItems) ? 1 : 0;
     return HFUSE_OK;
 }
 
@@ -71,6 +75,8 @@ int prep_maxpool(HFUSE_MAXPOOL_PARAMS(), MaxPoolArgs& a) {
     a.wide = aligned32(idx) ? 1 : 0;
     a.div_p4 = make_fastdiv(a.mode == 1 ? (uint32_t)(pW / 4) : 1u);
     a.div_ph = make_fastdiv((uint32_t)pH);
+    a.div_pw = make_fastdiv((uint32_t)pW);
+    a.small = ((long long)N * C * pH * pW <= kMaxItems) ? 1 : 0;
     return HFUSE_OK;
 }
 
@@ -112,6 +118,10 @@ int prep_upsample(HFUSE_UPSAMPLE_PARAMS(), UpsampleArgs& a) {
     a.wide = aligned32(out) ? 1 : 0;
     a.div_w4 = make_fastdiv(a.mode == 2 ? (uint32_t)(W / 4) : 1u);
     a.div_j = make_fastdiv((uint32_t)H + 1u);
+    a.div_ow4 = make_fastdiv(a.mode == 1 ? (uint32_t)(outW / 4) : 1u);
+    a.div_oh = make_fastdiv((uint32_t)outH);
+    a.div_ow = make_fastdiv((uint32_t)outW);
+    a.small = ((long long)N * C * outH * outW <= kMaxItems) ? 1 : 0;
     return HFUSE_OK;
 }
 

@@ -31,6 +31,8 @@ struct Im2colArgs {
     int mode;   // 0 = generic (one output element per item), 1 = 3x3 stride-1 tile path (4 columns per item),
                 // 2 = the same with 8 columns per item and 256-bit stores (pad 1, Wc % 8 == 0, col 32-byte aligned)
     FastDiv div_w4, div_hc;   // tile paths: by Wc/4 (mode 1) or Wc/8 (mode 2), and by Hc
+    FastDiv div_wc, div_taps, div_kw;   // generic path with fewer than 2^31 outputs (small != 0)
+    int small;
 };
 
 struct Im2colRole {
@@ -151,6 +153,23 @@ struct Im2colRole {
 
     template <int T>
     static __device__ __forceinline__ void run_generic(const Args& a, const RoleCtx& ctx) {
+        if (a.small) {      // every index fits 31 bits: multiply-high divisions only
+            const unsigned total = (unsigned)a.N * a.C * a.kh * a.kw * a.Hc * a.Wc;
+            for (unsigned e = (unsigned)ctx.block * T + ctx.tid; e < total; e += (unsigned)ctx.nblocks * T) {
+                unsigned w, h, tap, j;
+                unsigned r = fast_divmod(e, a.div_wc, w);
+                r = fast_divmod(r, a.div_hc, h);
+                const unsigned plane = fast_divmod(r, a.div_taps, tap);
+                const unsigned i = fast_divmod(tap, a.div_kw, j);
+                const int hi = (int)h * a.sh - a.ph + (int)i * a.dh;
+                const int wi = (int)w * a.sw - a.pw + (int)j * a.dw;
+                float v = 0.f;
+                if (hi >= 0 && hi < a.H && wi >= 0 && wi < a.W)
+                    v = __ldg(a.im + (size_t)plane * a.H * a.W + (size_t)hi * a.W + wi);
+                stg_stream1(a.col + e, v);
+            }
+            return;
+        }
         const unsigned long long plane_out = (unsigned long long)a.Hc * a.Wc;
         const unsigned long long taps = (unsigned long long)a.kh * a.kw;
         const unsigned long long total = (unsigned long long)a.N * a.C * taps * plane_out;
@@ -192,6 +211,8 @@ struct MaxPoolArgs {
     int mode;   // 0 = generic, 1 = 2x2 stride 2 without padding, pW % 4 == 0, W % 4 == 0
     FastDiv div_p4, div_ph;   // 2x2 path: by pW/4 and by pH
     int wide;                 // idx is 32-byte aligned: one 256-bit store for the four indices
+    FastDiv div_pw;           // generic path with fewer than 2^31 outputs (small != 0): by pW (and div_ph by pH)
+    int small;
 };
 
 __device__ __forceinline__ void pool_take(float v, int at, float& best, int& best_at) {
@@ -244,10 +265,19 @@ struct MaxPoolRole {
         const unsigned long long total = (unsigned long long)a.N * a.C * a.pH * a.pW;
         for (unsigned long long e = (unsigned long long)ctx.block * T + ctx.tid; e < total;
              e += (unsigned long long)ctx.nblocks * T) {
-            const int ow = (int)(e % a.pW);
-            unsigned long long r = e / a.pW;
-            const int oh = (int)(r % a.pH);
-            const unsigned long long plane = r / a.pH;
+            int ow, oh;
+            unsigned long long plane;
+            if (a.small) {
+                unsigned uw, uh;
+                const unsigned r = fast_divmod((unsigned)e, a.div_pw, uw);
+                plane = fast_divmod(r, a.div_ph, uh);
+                ow = (int)uw; oh = (int)uh;
+            } else {
+                ow = (int)(e % a.pW);
+                const unsigned long long r = e / a.pW;
+                oh = (int)(r % a.pH);
+                plane = r / a.pH;
+            }
             int hstart = oh * a.sh - a.ph;
             int wstart = ow * a.sw - a.pw;
             const int hend = min(hstart + (a.kh - 1) * a.dh + 1, a.H);
@@ -284,6 +314,8 @@ struct UpsampleArgs {
                 // 2 = exact x2 strip path (run_x2)
     FastDiv div_w4, div_j;   // x2 path: by W/4 and by H+1
     int wide;                // output is 32-byte aligned: 256-bit stores
+    FastDiv div_ow4, div_oh, div_ow;   // 4-wide path: by outW/4 and outH; scalar path (small != 0): by outW and outH
+    int small;
 };
 
 __device__ __forceinline__ void bilinear_src(float scale, int dst, int align, int in_size, int& i1, int& i1p,
@@ -321,10 +353,9 @@ struct UpsampleRole {
         const unsigned oH = (unsigned)a.outH;
         const unsigned total = (unsigned)a.N * a.C * oH * W4;      // host guarantees < 2^31
         for (unsigned it = (unsigned)ctx.block * T + ctx.tid; it < total; it += (unsigned)ctx.nblocks * T) {
-            const unsigned w4 = it % W4;
-            const unsigned r = it / W4;
-            const unsigned h2 = r % oH;
-            const unsigned plane = r / oH;
+            unsigned w4, h2;
+            const unsigned r = fast_divmod(it, a.div_ow4, w4);
+            const unsigned plane = fast_divmod(r, a.div_oh, h2);
             int h1, h1p;
             float h0l, h1l;
             bilinear_src(a.rheight, (int)h2, a.align_corners, a.H, h1, h1p, h0l, h1l);
@@ -427,10 +458,19 @@ struct UpsampleRole {
         const unsigned long long total = (unsigned long long)a.N * a.C * a.outH * a.outW;
         for (unsigned long long e = (unsigned long long)ctx.block * T + ctx.tid; e < total;
              e += (unsigned long long)ctx.nblocks * T) {
-            const int w2 = (int)(e % a.outW);
-            unsigned long long r = e / a.outW;
-            const int h2 = (int)(r % a.outH);
-            const unsigned long long plane = r / a.outH;
+            int w2, h2;
+            unsigned long long plane;
+            if (a.small) {
+                unsigned uw, uh;
+                const unsigned r = fast_divmod((unsigned)e, a.div_ow, uw);
+                plane = fast_divmod(r, a.div_oh, uh);
+                w2 = (int)uw; h2 = (int)uh;
+            } else {
+                w2 = (int)(e % a.outW);
+                const unsigned long long r = e / a.outW;
+                h2 = (int)(r % a.outH);
+                plane = r / a.outH;
+            }
             int h1, h1p, w1, w1p;
             float h0l, h1l, w0l, w1l;
             bilinear_src(a.rheight, h2, a.align_corners, a.H, h1, h1p, h0l, h1l);
