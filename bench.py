@@ -219,6 +219,31 @@ def extras(torch, ops, crypto, workloads, dev, steps, warmup, peak, barrier):
             "frac_of_hbm_peak": round(nbytes / tf / 1e6 / peak, 3), "algorithmic_bytes": nbytes}
         del sets
         torch.cuda.empty_cache()
+    # the three histc pairs the benchmark description names besides configuration 2
+    w0, w1, w2 = workloads.config0(), workloads.config1(), workloads.config2()
+    hist_bytes = w2["hist"].numel() * 4 + 1024
+
+    def other(key):
+        if key == "maxpool":
+            return ops.MaxPool(w0["pool"].to(dev), **w0["maxpool"]), 89_915_392
+        if key == "upsample":
+            return ops.Upsample(w1["up"].to(dev), scale_factor=2), 128_450_560
+        return ops.BnStats(w1["bn"].to(dev), w1["eps"]), 25_692_160
+    for key in ("maxpool", "upsample", "bnstats"):
+        sets, nbytes = [], 0
+        for _ in range(4):
+            b, ob = other(key)
+            sets.append((ops.Histc(w2["hist"].to(dev), w2["bins"], w2["lo"], w2["hi"]), b))
+            nbytes = hist_bytes + ob
+        tf, tb, ta, t2, tv = measure_dl_pair(torch, ops, sets, steps, warmup, barrier)
+        out[f"histc_{key}"] = {
+            "fused_us": round(tf * 1e3, 2), "back_to_back_us": round(tb * 1e3, 2),
+            "vertical_fusion_us": round(tv * 1e3, 2), "first_alone_us": round(ta * 1e3, 2),
+            "second_alone_us": round(t2 * 1e3, 2), "speedup_vs_back_to_back": round(tb / tf, 3),
+            "GB_per_s": round(nbytes / tf / 1e6, 1), "frac_of_hbm_peak": round(nbytes / tf / 1e6 / peak, 3),
+            "algorithmic_bytes": nbytes}
+        del sets
+        torch.cuda.empty_cache()
     csteps = 2
     c3 = workloads.config3()
     a = crypto.Blake256(c3["blake_header"], c3["start"], c3["count"], c3["target"])
@@ -226,10 +251,12 @@ def extras(torch, ops, crypto, workloads, dev, steps, warmup, peak, barrier):
     tf = time_region(torch, lambda i: crypto.run_pair(a, b), csteps, 1, barrier) / csteps
     hits_f = (a.result(), b.result())
     tb = time_region(torch, lambda i: crypto.run_back_to_back(a, b), csteps, 1, barrier) / csteps
+    cpu3 = cpu_hash_rates(c3["blake_header"], c3["sha_header"], c3["target"])
     out["cfg3_blake256_sha256d"] = {
         "nonces_each": c3["count"], "fused_ms": round(tf, 2), "back_to_back_ms": round(tb, 2),
         "speedup_vs_back_to_back": round(tb / tf, 3), "GH_per_s_each_fused": round(c3["count"] / tf / 1e6, 3),
-        "hits": [hits_f[0][0], hits_f[1][0]], "fused_equals_unfused": hits_f == (a.result(), b.result())}
+        "hits": [hits_f[0][0], hits_f[1][0]], "fused_equals_unfused": hits_f == (a.result(), b.result()),
+        "cpu_baseline": cpu3}
     c4 = workloads.config4(dev)
     s = crypto.Sia(c4["sia_header"], c4["start"], c4["count"], c4["target"])
     e = crypto.Ethash(c4["dag"], c4["header_hash"], c4["start"], c4["count"], c4["target"])
@@ -242,7 +269,32 @@ def extras(torch, ops, crypto, workloads, dev, steps, warmup, peak, barrier):
         "speedup_vs_back_to_back": round(tb / tf, 3), "ethash_MH_per_s_fused": round(c4["count"] / tf / 1e3, 1),
         "ethash_MH_per_s_alone": round(c4["count"] / te / 1e3, 1),
         "ethash_frac_of_hbm_peak_fused": round(c4["count"] * ETHASH_BYTES_PER_HASH / tf / 1e6 / peak, 3),
-        "hits": [hits_f[0][0], hits_f[1][0]], "fused_equals_unfused": hits_f == (s.result(), e.result())}
+        "hits": [hits_f[0][0], hits_f[1][0]], "fused_equals_unfused": hits_f == (s.result(), e.result()),
+        "cpu_baseline": cpu_ethash_sia_rates(c4)}
+    return out
+
+
+def cpu_hash_rates(blake_header, sha_header, target, n=1 << 21):
+    """CPU restatement (C, OpenMP over nonces, all host threads) on a bounded sample of 2^21 nonces."""
+    from oracle import crypto as OC
+    out = {"cores": OC.num_threads(), "kind": "port", "sample": f"{n} nonces per hash"}
+    for kind, name, hdr in ((0, "blake256", blake_header), (1, "sha256d", sha_header)):
+        t0 = time.perf_counter()
+        OC.search(kind, hdr, 0, n, target)
+        out[name + "_MH_per_s"] = round(n / (time.perf_counter() - t0) / 1e6, 2)
+    return out
+
+
+def cpu_ethash_sia_rates(c4, n_eth=1 << 17, n_sia=1 << 21):
+    from oracle import crypto as OC
+    dag = c4["dag"].cpu().numpy()
+    out = {"cores": OC.num_threads(), "kind": "port", "sample": f"{n_eth} ethash nonces over the 1 GiB DAG, {n_sia} Sia nonces"}
+    t0 = time.perf_counter()
+    OC.search(3, c4["header_hash"], 0, n_eth, c4["target"], dag=dag)
+    out["ethash_MH_per_s"] = round(n_eth / (time.perf_counter() - t0) / 1e6, 3)
+    t0 = time.perf_counter()
+    OC.search(2, c4["sia_header"], 0, n_sia, c4["target"])
+    out["sia_MH_per_s"] = round(n_sia / (time.perf_counter() - t0) / 1e6, 2)
     return out
 
 
