@@ -128,12 +128,15 @@ int prep_eth(HFUSE_ETHASH_PARAMS(), EthashArgs& a) {
 
 // ---- variants: (index, T1, T2, minBlocks/SM).  The reference has a single 128:128 split for
 // the crypto pairs (all four kernels use 128-thread blocks, configs/crypto_kernels.yaml);
-// unequal splits are added because the halves are far from equally expensive.
+// unequal splits, down to one warp in eight, are added because the halves are far from equally
+// expensive: next to ethash, an ALU-bound hash is best given a small range that fills the ALU gaps
+// while ethash keeps nearly all of its loads in flight.
 #define CRYPTO_PAIR_VARIANTS(X)                                                                       \
     X(0, 128, 128, 2) X(1, 128, 128, 3) X(2, 128, 128, 4) X(3, 256, 128, 2) X(4, 128, 256, 2)         \
     X(5, 384, 128, 1) X(6, 128, 384, 1) X(7, 256, 256, 1) X(8, 256, 256, 2) X(9, 128, 128, 1)         \
-    X(10, 384, 128, 2) X(11, 128, 384, 2) X(12, 256, 128, 1) X(13, 128, 256, 1)
-constexpr int kCryptoPairVariants = 14;
+    X(10, 384, 128, 2) X(11, 128, 384, 2) X(12, 256, 128, 1) X(13, 128, 256, 1)         \
+    X(14, 64, 448, 1) X(15, 448, 64, 1) X(16, 64, 192, 2) X(17, 192, 64, 2) X(18, 32, 224, 4) X(19, 224, 32, 4)
+constexpr int kCryptoPairVariants = 20;
 #define CRYPTO_SOLO_VARIANTS(X) \
     X(0, 128, 4) X(1, 128, 6) X(2, 128, 8) X(3, 256, 2) X(4, 256, 3) X(5, 256, 4) X(6, 128, 3) X(7, 128, 5) X(8, 128, 2)
 constexpr int kCryptoSoloVariants = 9;
