@@ -46,6 +46,19 @@ CFG1_BYTES = 154_142_720
 CFG0_BYTES = 218_365_952
 CFG2_BYTES = 324_011_008
 ETHASH_BYTES_PER_HASH = 8192
+# 32-bit operations per nonce, counted from the specifications.
+# SPEC_OPS: every add, xor, rotate and boolean separate (no three-input adds, no merged logic):
+#   BLAKE-256   14 rounds x 8 G x (6 add + 6 xor + 4 rotate)
+#   SHA-256d    2 compressions x (64 rounds x 25 + 48 schedule words x 13)
+#   BLAKE2b     12 rounds x 8 G x (6 add + 4 xor + 4 rotate) on 64-bit words = 2 x 32-bit each
+# LOGIC_OPS: what is left for the logic/shift pipe when adds issue elsewhere and three-input
+# logic is merged (a SHA-256 Sigma = 3 funnel shifts + 1 three-input xor, Ch and Maj = 1 each;
+# the message-word xors of BLAKE are precomputed): the pipe that saturates first.
+#   BLAKE-256   14 x 8 x (4 xor + 4 rotate)
+#   SHA-256d    2 x (64 x 10 + 48 x 8)
+#   BLAKE2b     12 x 8 x (4 xor x 2 halves + rotations 32/24/16/63 = 0 + 2 + 2 + 2)
+SPEC_OPS_PER_HASH = {"blake256": 14 * 8 * 16, "sha256d": 2 * (64 * 25 + 48 * 13), "sia": 12 * 8 * 14 * 2}
+LOGIC_OPS_PER_HASH = {"blake256": 14 * 8 * 8, "sha256d": 2 * (64 * 10 + 48 * 8), "sia": 12 * 8 * 14}
 
 
 def measured_peak_gbs():
@@ -205,6 +218,31 @@ def vertical_time(torch, ops, sets, steps, warmup):
     return best
 
 
+def int32_peak(torch, dev):
+    """Measured rate of independent 32-bit add/xor/rotate chains on every SM, in 10^12 lane
+    operations per second, for the three mixes of hfuse_int32_probe; `peak` is the best of them."""
+    import ctypes
+    from hfuse_b200 import _lib
+    sink = torch.zeros(1, dtype=torch.int32, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    out = {}
+    for mix, name in ((0, "xor_rot"), (1, "add_xor_rot"), (2, "add_xor_rot_fma_add")):
+        n = ctypes.c_uint64(0)
+        best = 0.0
+        for it in range(4):  # the first launch warms up
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _lib.check(_lib.lib().hfuse_int32_probe(mix, 4096, sink.data_ptr(), ctypes.byref(n), st), "hfuse_int32_probe")
+            e1.record()
+            e1.synchronize()
+            if it:
+                best = max(best, n.value / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+        out[name + "_Tops"] = round(best, 2)
+    out["peak_Tops"] = max(out.values())
+    out["logic_pipe_peak_Tops"] = out["xor_rot_Tops"]
+    return out
+
+
 def extras(torch, ops, crypto, workloads, dev, steps, warmup, peak, barrier):
     """Fused vs back-to-back for every benchmark configuration (N = 1 only)."""
     out = {}
@@ -252,7 +290,16 @@ def extras(torch, ops, crypto, workloads, dev, steps, warmup, peak, barrier):
     hits_f = (a.result(), b.result())
     tb = time_region(torch, lambda i: crypto.run_back_to_back(a, b), csteps, 1, barrier) / csteps
     cpu3 = cpu_hash_rates(c3["blake_header"], c3["sha_header"], c3["target"])
+    ipeak = int32_peak(torch, dev)
+    out["int32_peak"] = ipeak
+    ops3 = (SPEC_OPS_PER_HASH["blake256"] + SPEC_OPS_PER_HASH["sha256d"]) * c3["count"]
+    lops3 = (LOGIC_OPS_PER_HASH["blake256"] + LOGIC_OPS_PER_HASH["sha256d"]) * c3["count"]
     out["cfg3_blake256_sha256d"] = {
+        "spec_int32_ops_per_nonce_pair": SPEC_OPS_PER_HASH["blake256"] + SPEC_OPS_PER_HASH["sha256d"],
+        "spec_Tops_fused": round(ops3 / tf / 1e9, 2),
+        "logic_ops_per_nonce_pair": LOGIC_OPS_PER_HASH["blake256"] + LOGIC_OPS_PER_HASH["sha256d"],
+        "logic_Tops_fused": round(lops3 / tf / 1e9, 2),
+        "frac_of_logic_pipe_peak": round(lops3 / tf / 1e9 / ipeak["logic_pipe_peak_Tops"], 3),
         "nonces_each": c3["count"], "fused_ms": round(tf, 2), "back_to_back_ms": round(tb, 2),
         "speedup_vs_back_to_back": round(tb / tf, 3), "GH_per_s_each_fused": round(c3["count"] / tf / 1e6, 3),
         "hits": [hits_f[0][0], hits_f[1][0]], "fused_equals_unfused": hits_f == (a.result(), b.result()),

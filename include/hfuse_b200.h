@@ -305,6 +305,14 @@ HFUSE_API int hfuse_tune_describe(const char* pair, int variant, char* buf, size
  * little-endian u64 words) — the generator the synthetic DAG and headers are drawn from. */
 HFUSE_API void hfuse_xoshiro256ss_fill(uint64_t seed, void* host_dst, size_t nbytes);
 
+/* Measurement utility (no counterpart in the reference): one launch of a kernel that does
+ * nothing but independent 32-bit add / xor / rotate chains on every SM, the operation mix of
+ * the hash searches.  mix 0 = xor + rotate, 1 = add + xor + rotate on the integer pipe,
+ * 2 = the same with the add issued as a multiply-add (the arrangement the hash roles use).
+ * Writes the number of 32-bit lane operations the launch performs to *lane_ops (host); the
+ * caller times the launch and divides.  `sink` is 4 device bytes that are never written. */
+HFUSE_API int hfuse_int32_probe(int mix, uint32_t iters, uint32_t* sink, uint64_t* lane_ops, hfuse_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -189,3 +189,19 @@ def test_fused_search_without_a_reset_still_sweeps_everything(dev, kat):
     assert first[0] > 0 and first[1] > 0
     crypto.run_pair(a, b, reset=False)
     assert (a.result()[0], b.result()[0]) == (2 * first[0], 2 * first[1])
+
+
+def test_int32_probe_reports_its_operation_count_and_rejects_bad_arguments(dev):
+    import ctypes
+    sink = torch.zeros(1, dtype=torch.int32, device=dev)
+    n = ctypes.c_uint64(0)
+    L = _lib.lib()
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    for mix, per in ((0, 2), (1, 3), (2, 3)):
+        assert L.hfuse_int32_probe(mix, 64, sink.data_ptr(), ctypes.byref(n), None) == 0
+        assert n.value == sms * 8 * 256 * 64 * 16 * per
+    torch.cuda.synchronize()
+    assert int(sink.item()) == 0
+    assert L.hfuse_int32_probe(3, 64, sink.data_ptr(), ctypes.byref(n), None) == -1
+    assert L.hfuse_int32_probe(0, 0, sink.data_ptr(), ctypes.byref(n), None) == -1
+    assert L.hfuse_int32_probe(0, 64, None, ctypes.byref(n), None) == -1
