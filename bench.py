@@ -429,6 +429,12 @@ def run_ours(args):
         dist.all_reduce(ok_flag, op=dist.ReduceOp.MIN)
         if ok_flag.item() == 0:
             ex = None
+    if args.pair_variant >= 0:
+        _lib.tune_set("upsample_bnstats_allreduce" if ex is not None else "upsample_bnstats", args.pair_variant, 0)
+    if args.share_permille >= 0 and ex is not None:
+        _lib.tune_set_share("upsample_bnstats_allreduce", args.share_permille)
+    if args.tune_share:
+        return run_tune_share(args, torch, _lib, ex, sets, NSETS, dev, rank, barrier, use_dist)
     if ex is not None:
         collective = "in-kernel sum of the [256,3] f64 moments over NVLink peer stores"
 
@@ -652,6 +658,60 @@ def run_ours(args):
         print(json.dumps(line), flush=True)
     if use_dist:
         shutdown(torch, graph)
+
+
+def run_tune_share(args, torch, _lib, ex, sets, nsets, dev, rank, barrier, use_dist):
+    """Sweep of the exchange pair (upsample + statistics + in-kernel all-reduce) over thread splits
+    and over the share of the upsample that the statistics range takes over, at the launched
+    number of ranks; the time of a step is the maximum over ranks.  Rank 0 prints one JSON object."""
+    from hfuse_b200.exchange import BnExchange
+    if ex is None:
+        ex = BnExchange(256)            # world of one (or NCCL fallback refused): the local buffer
+    name = "upsample_bnstats_allreduce"
+    descr = _lib.tune_variants(name)
+    variants = [v for v, d in enumerate(descr) if ":0:" not in d]
+    shares = (0, 100, 200, 300, 400, 500)
+    reps, gsteps = 6, 4 * nsets
+    table = {}
+    for v in variants:
+        row = {}
+        for share in shares:
+            _lib.tune_set(name, v, 0)
+            _lib.tune_set_share(name, share)
+            for i in range(nsets):
+                ex.run_pair(*sets[i])
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                for i in range(gsteps):
+                    ex.run_pair(*sets[i % nsets])
+            graph.replay()
+            torch.cuda.synchronize()
+            barrier()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(reps):
+                graph.replay()
+            e.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([s.elapsed_time(e)], dtype=torch.float64, device=dev)
+            if use_dist:
+                import torch.distributed as dist
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            row[str(share)] = round(float(t.item()) / (reps * gsteps) * 1e3, 2)
+            del graph
+        table[descr[v]] = row
+    _lib.tune_set(name, -1, 0)
+    _lib.tune_set_share(name, -1)
+    timed_out = ex.timed_out()
+    if rank == 0:
+        best = min(((t, d, sh) for d, row in table.items() for sh, t in row.items()))
+        print(json.dumps({"pair": name, "n_gpus": args.gpus, "unit": "us per step, max over ranks",
+                          "best": {"variant": best[1], "index": descr.index(best[1]), "share_permille": int(best[2]), "us": best[0]},
+                          "exchange_timed_out": timed_out, "table": table}))
+    if use_dist:
+        shutdown(torch, None)
+    ex.close()
 
 
 def crypto_sharded(torch, crypto, sharding, workloads, dev, rank, world, barrier):
@@ -918,6 +978,13 @@ def main():
     ap.add_argument("--count", type=int, default=1 << 24, help="nonces per step with --only cfg3|cfg4")
     ap.add_argument("--dag-items", type=int, default=8_388_608)
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--pair-variant", type=int, default=-1,
+                    help="force thread-range variant V of the headline pair (tuning aid; default: the compiled-in choice)")
+    ap.add_argument("--tune-share", action="store_true",
+                    help="sweep thread splits x upsample shares of the exchange pair at the launched number of ranks")
+    ap.add_argument("--share-permille", type=int, default=-1,
+                    help="N > 1, fused collective: share of the upsample that the statistics thread range takes over "
+                         "while the moments travel (tuning aid; default: the compiled-in choice)")
     ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
                     help="N > 1: sum the batch-norm moments inside the fused kernel (peer memory) or with NCCL")
     ap.add_argument("--no-graph", action="store_true", help="time direct launches instead of CUDA-graph replays")

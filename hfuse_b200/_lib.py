@@ -67,7 +67,7 @@ def exported_symbols() -> list[str]:
     names += ["hfuse_maxpool2d_backward_f32", "hfuse_bn_backward_f32", "hfuse_maxpool_backward_bn_backward_f32"]
     names += ["hfuse_error_string", "hfuse_version", "hfuse_bnstats_workspace_bytes", "hfuse_bnstats_noalloc_f32",
               "hfuse_bnstats_finalize_f64", "hfuse_hits_reset", "hfuse_hash_batch", "hfuse_tune_set",
-              "hfuse_tune_describe", "hfuse_xoshiro256ss_fill", "hfuse_int32_probe"]
+              "hfuse_tune_describe", "hfuse_tune_set_share", "hfuse_xoshiro256ss_fill", "hfuse_int32_probe"]
     return names
 
 
@@ -130,6 +130,7 @@ def lib() -> C.CDLL:
     L.hfuse_hash_batch.argtypes = [_i, C.c_char_p, _p, _u32, _u64, _u32, _p, _p, _p]
     L.hfuse_tune_set.restype, L.hfuse_tune_set.argtypes = _i, [C.c_char_p, _i, _i]
     L.hfuse_tune_describe.restype, L.hfuse_tune_describe.argtypes = _i, [C.c_char_p, _i, C.c_char_p, _sz]
+    L.hfuse_tune_set_share.restype, L.hfuse_tune_set_share.argtypes = _i, [C.c_char_p, _i]
     L.hfuse_xoshiro256ss_fill.restype, L.hfuse_xoshiro256ss_fill.argtypes = None, [_u64, _p, _sz]
     L.hfuse_int32_probe.restype, L.hfuse_int32_probe.argtypes = _i, [_i, _u32, _p, C.POINTER(C.c_uint64), _p]
     _lib = L
@@ -147,6 +148,10 @@ def check(code: int, where: str) -> None:
 
 def tune_set(name: str, variant: int = -1, blocks_per_sm: int = 0) -> None:
     check(lib().hfuse_tune_set(name.encode(), variant, blocks_per_sm), f"tune_set({name})")
+
+
+def tune_set_share(name: str, permille: int = -1) -> None:
+    check(lib().hfuse_tune_set_share(name.encode(), permille), f"tune_set_share({name})")
 
 
 def tune_variants(name: str) -> list[str]:

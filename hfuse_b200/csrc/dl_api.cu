@@ -65,7 +65,7 @@ int dl_describe(const char* name, int variant, char* buf, size_t n) {
     static const char* solos[] = {"im2col", "maxpool", "bnstats", "upsample", "histc"};
     static const char* pairs[] = {"im2col_maxpool", "im2col_bnstats", "im2col_histc", "im2col_upsample",
                                   "maxpool_bnstats", "maxpool_upsample", "histc_maxpool", "histc_upsample",
-                                  "upsample_bnstats", "histc_bnstats"};
+                                  "upsample_bnstats", "histc_bnstats", "upsample_bnstats_allreduce"};
     for (const char* s : solos)
         if (!strcmp(s, name)) return describe_dl_solo(variant, buf, n);
     for (const char* p : pairs)

@@ -122,8 +122,12 @@ int hfuse_upsample_bnstats_allreduce_f32(HFUSE_UPSAMPLE_PARAMS(a_), HFUSE_BNSTAT
     if (int rc = prep_upsample(UPSAMPLE_NAMES(a_), a)) return rc;
     if (int rc = prep_bnstats(BNSTATS_NAMES(b_), b)) return rc;
     if (int rc = next_use(ex, b_C, b.xchg)) return rc;
-    return dispatch_pair<UpsampleRole, BnStatsXchgRole>("upsample_bnstats", kDefaultPair_upsample_bnstats, a, b,
-                                                        S_(stream));
+    // Its own tuning entry.  The statistics range sends its moments, then works through a share of
+    // the upsample and only then waits for the peers, so the best split gives that range more
+    // threads than the single-GPU pair does (it should finish its own work early).
+    return dispatch_pair_share<UpsampleRole, BnStatsXchgRole>("upsample_bnstats_allreduce",
+                                                              kDefaultPair_upsample_bnstats_allreduce,
+                                                              kDefaultShare_upsample_bnstats_allreduce, a, b, S_(stream));
 }
 
 }  // extern "C"

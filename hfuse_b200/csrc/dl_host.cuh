@@ -156,10 +156,10 @@ template <class A> int pre_launch(const A&, cudaStream_t) { return HFUSE_OK; }
     X(0, 256, 256, 2) X(1, 384, 128, 2) X(2, 128, 384, 2) X(3, 256, 256, 3) X(4, 512, 512, 1)       \
     X(5, 768, 256, 1) X(6, 256, 768, 1) X(7, 640, 384, 1) X(8, 384, 640, 1) X(9, 512, 256, 1)       \
     X(10, 256, 512, 1) X(11, 128, 128, 4) X(12, 128, 128, 6) X(13, 896, 128, 1) X(14, 128, 896, 1)  \
-    X(15, 512, 256, 2) X(16, 256, 512, 2)
+    X(15, 512, 256, 2) X(16, 256, 512, 2) X(20, 384, 256, 2) X(21, 256, 384, 2)
 // vertical fusion (the reference's vfuse presets): (index, T, minBlocks/SM), described as "T:0:minBlocks"
 #define DL_VPAIR_VARIANTS(X) X(17, 512, 2) X(18, 1024, 1) X(19, 256, 4)
-constexpr int kDlPairVariants = 20;
+constexpr int kDlPairVariants = 22;
 
 #define DL_SOLO_VARIANTS(X) X(0, 256, 4) X(1, 256, 8) X(2, 512, 2) X(3, 128, 8) X(4, 512, 4) X(5, 1024, 1) X(6, 128, 16)
 constexpr int kDlSoloVariants = 7;
@@ -173,6 +173,28 @@ int dispatch_pair(const char* name, int default_variant, typename RA::Args a, ty
     switch (v) {
 #define X(I, TA, TB, MB) \
     case I: return launch_pair<RA, RB, TA, TB, MB>(a, b, t.blocks_per_sm, s);
+        DL_PAIR_VARIANTS(X)
+#undef X
+#define X(I, T, MB) \
+    case I: return launch_vpair<RA, RB, T, MB>(a, b, t.blocks_per_sm, s);
+        DL_VPAIR_VARIANTS(X)
+#undef X
+    }
+    return HFUSE_ERR_BAD_ARG;
+}
+
+// pairs whose second role takes over a share of the first role's items (launch_pair_share)
+template <class RA, class RB>
+int dispatch_pair_share(const char* name, int default_variant, int default_share, typename RA::Args a,
+                        typename RB::Args b, cudaStream_t s) {
+    const Tune t = tune_get(name);
+    const int v = t.variant >= 0 ? t.variant : default_variant;
+    const int share = t.share_permille >= 0 ? t.share_permille : default_share;
+    if (int rc = pre_launch(a, s)) return rc;
+    if (int rc = pre_launch(b, s)) return rc;
+    switch (v) {
+#define X(I, TA, TB, MB) \
+    case I: return launch_pair_share<RA, RB, TA, TB, MB>(a, b, t.blocks_per_sm, share, s);
         DL_PAIR_VARIANTS(X)
 #undef X
 #define X(I, T, MB) \

@@ -347,12 +347,23 @@ struct UpsampleRole {
     static int smem_bytes(const Args&, int) { return 0; }
     static int plan(Args&, int, int) { return 0; }
 
+    // Items of the vector paths (the scalar path counts in 64 bits and is never split):
+    // the 4-wide path works on N*C*outH*(outW/4) items, the x2 strip path on N*C*(H+1)*(W/4).
+    static __host__ __device__ __forceinline__ unsigned vec_items(const Args& a) {
+        return a.mode == 2 ? (unsigned)a.N * a.C * ((unsigned)a.H + 1) * ((unsigned)a.W >> 2)
+                           : (unsigned)a.N * a.C * (unsigned)a.outH * ((unsigned)a.outW >> 2);
+    }
+    // A range of items handed to another thread range must start on a row boundary (the x2
+    // path reads its left and right neighbours' columns from the adjacent lanes).
+    static __host__ __device__ __forceinline__ unsigned vec_row_items(const Args& a) {
+        return a.mode == 2 ? (unsigned)a.W >> 2 : (unsigned)a.outW >> 2;
+    }
+
     template <int T>
-    static __device__ __forceinline__ void run_vec4(const Args& a, const RoleCtx& ctx) {
+    static __device__ __forceinline__ void run_vec4(const Args& a, const RoleCtx& ctx, unsigned begin, unsigned end) {
         const unsigned W4 = (unsigned)a.outW >> 2;
         const unsigned oH = (unsigned)a.outH;
-        const unsigned total = (unsigned)a.N * a.C * oH * W4;      // host guarantees < 2^31
-        for (unsigned it = (unsigned)ctx.block * T + ctx.tid; it < total; it += (unsigned)ctx.nblocks * T) {
+        for (unsigned it = begin + (unsigned)ctx.block * T + ctx.tid; it < end; it += (unsigned)ctx.nblocks * T) {
             unsigned w4, h2;
             const unsigned r = fast_divmod(it, a.div_ow4, w4);
             const unsigned plane = fast_divmod(r, a.div_oh, h2);
@@ -382,13 +393,12 @@ struct UpsampleRole {
     // (four 16-byte stores).  Every product and sum is the one the generic
     // path computes, so both paths give the same bits.
     template <int T>
-    static __device__ __forceinline__ void run_x2(const Args& a, const RoleCtx& ctx) {
+    static __device__ __forceinline__ void run_x2(const Args& a, const RoleCtx& ctx, unsigned begin, unsigned total) {
         const unsigned W4 = (unsigned)a.W >> 2;
-        const unsigned J = (unsigned)a.H + 1;                        // row pairs per plane
-        const unsigned total = (unsigned)a.N * a.C * J * W4;         // host guarantees < 2^31
         const unsigned lane = ctx.tid & 31;
-        // warp-uniform trip count: every lane takes part in the shuffles
-        for (unsigned base = (unsigned)ctx.block * T + (ctx.tid & ~31); base < total;
+        // items [begin, total), both multiples of W4 (row pairs of W4 items; the host guarantees
+        // fewer than 2^31 in all); warp-uniform trip count: every lane takes part in the shuffles
+        for (unsigned base = begin + (unsigned)ctx.block * T + (ctx.tid & ~31); base < total;
              base += (unsigned)ctx.nblocks * T) {
             const bool live = base + lane < total;
             const unsigned it = live ? base + lane : total - 1;
@@ -484,9 +494,19 @@ struct UpsampleRole {
 
     template <int T, int BAR>
     static __device__ __forceinline__ void run(const Args& a, const RoleCtx& ctx) {
-        if (a.mode == 2) run_x2<T>(a, ctx);
-        else if (a.mode == 1) run_vec4<T>(a, ctx);
+        if (a.mode == 2) run_x2<T>(a, ctx, 0u, vec_items(a));
+        else if (a.mode == 1) run_vec4<T>(a, ctx, 0u, vec_items(a));
         else run_scalar<T>(a, ctx);
+    }
+
+    // Items [begin, end) of a vector path, for a kernel that hands part of the work to another
+    // thread range (begin and end on row boundaries).  The scalar path is not split: the
+    // caller passes begin = 0 to the range that owns it and an empty range to the other.
+    template <int T>
+    static __device__ __forceinline__ void run_range(const Args& a, const RoleCtx& ctx, unsigned begin, unsigned end) {
+        if (a.mode == 2) { if (begin < end) run_x2<T>(a, ctx, begin, end); }
+        else if (a.mode == 1) run_vec4<T>(a, ctx, begin, end);
+        else if (begin == 0u && end != 0u) run_scalar<T>(a, ctx);
     }
 };
 
@@ -767,9 +787,9 @@ struct BnStatsRole {
         }
     }
 
-    // Exchange form of finish(), run by all 32 lanes of one warp with the channel's local
-    // moments in lane 0: send them to every rank, collect every rank's, fold in rank order.
-    static __device__ __forceinline__ void exchange(const Args& a, int c, Moments m, int lane) {
+    // Exchange form of finish(), in two halves, each run by all 32 lanes of one warp.
+    // xchg_send: the channel's local moments are in lane 0; lane r stores them into rank r's buffer.
+    static __device__ __forceinline__ void xchg_send(const Args& a, int c, Moments m, int lane) {
         const BnXchg& x = a.xchg;
         const float mean_l = __shfl_sync(0xffffffffu, m.mean, 0);
         const float m2_l = __shfl_sync(0xffffffffu, m.m2, 0);
@@ -785,7 +805,12 @@ struct BnStatsRole {
             row[3] = tag | (s2 >> 32);
             row[4] = tag | (unsigned long long)(unsigned)((long long)a.N * a.HW);
         }
-        // lane r collects rank r's row from the local buffer
+    }
+
+    // xchg_collect: lane r waits (bounded) for rank r's row of channel c in the local buffer; the
+    // rows are folded in rank order and lane 0 writes the channel's global statistics.
+    static __device__ __forceinline__ void xchg_collect(const Args& a, int c, int lane) {
+        const BnXchg& x = a.xchg;
         double rs1 = 0.0, rs2 = 0.0, rn = 0.0;
         bool ok = true;
         if (lane < x.world) {
@@ -825,19 +850,33 @@ struct BnStatsRole {
         }
     }
 
-    // called by all 32 lanes of warp 0 with the channel's folded moments in lane 0
-    template <bool XCHG>
+    // called by all 32 lanes of warp 0 with the channel's folded moments in lane 0.  DEFER: send
+    // now, collect later (collect_deferred), so that the wait for the peers overlaps other work.
+    template <bool XCHG, bool DEFER>
     static __device__ __forceinline__ void complete(const Args& a, int c, Moments m, int lane) {
-        if (XCHG) exchange(a, c, m, lane);
-        else if (lane == 0) finish(a, c, m);
+        if (XCHG) {
+            xchg_send(a, c, m, lane);
+            if (!DEFER) xchg_collect(a, c, lane);
+        } else if (lane == 0) {
+            finish(a, c, m);
+        }
     }
 
     template <int T, int BAR>
     static __device__ __forceinline__ void run(const Args& a, const RoleCtx& ctx) {
-        run_impl<T, BAR, false>(a, ctx);
+        run_impl<T, BAR, false, false>(a, ctx);
     }
 
-    template <int T, int BAR, bool XCHG>
+    // The second half of run_impl<.., XCHG = true, DEFER = true>: warp 0 collects the channels whose
+    // moments this block sent.  Only the one-slice-per-channel plan defers (the block that owns a
+    // unit is then the one that sent it); with slices the exchange already happened in run_impl.
+    template <int T>
+    static __device__ __forceinline__ void collect_deferred(const Args& a, const RoleCtx& ctx) {
+        if (a.S != 1 || (ctx.tid >> 5) != 0) return;
+        for (unsigned u = ctx.block; u < (unsigned)a.C; u += ctx.nblocks) xchg_collect(a, (int)u, ctx.tid & 31);
+    }
+
+    template <int T, int BAR, bool XCHG, bool DEFER>
     static __device__ __forceinline__ void run_impl(const Args& a, const RoleCtx& ctx) {
         constexpr int NW = T / 32;
         constexpr int UNROLL = 4;
@@ -917,7 +956,7 @@ struct BnStatsRole {
             Moments w = (lane < NW) ? Moments{buf[lane], buf[NW + lane], buf[2 * NW + lane]} : Moments{0.f, 0.f, 0.f};
             w = warp_merge(w);
             if (a.S == 1) {
-                complete<XCHG>(a, (int)c, w, lane);
+                complete<XCHG, DEFER>(a, (int)c, w, lane);
                 continue;
             }
             // publish this slice; the block that takes the last ticket folds all slices
@@ -938,7 +977,7 @@ struct BnStatsRole {
                 }
                 q = warp_merge(q);
                 if (lane == 0) a.tickets[c] = 0u;     // ready for the next call
-                complete<XCHG>(a, (int)c, q, lane);
+                complete<XCHG, false>(a, (int)c, q, lane);
             }
         }
     }
@@ -948,7 +987,16 @@ struct BnStatsRole {
 struct BnStatsXchgRole : BnStatsRole {
     template <int T, int BAR>
     static __device__ __forceinline__ void run(const Args& a, const RoleCtx& ctx) {
-        BnStatsRole::run_impl<T, BAR, true>(a, ctx);
+        BnStatsRole::run_impl<T, BAR, true, false>(a, ctx);
+    }
+    // the two halves for a kernel that puts other work between sending and collecting
+    template <int T, int BAR>
+    static __device__ __forceinline__ void run_early(const Args& a, const RoleCtx& ctx) {
+        BnStatsRole::run_impl<T, BAR, true, true>(a, ctx);
+    }
+    template <int T, int BAR>
+    static __device__ __forceinline__ void run_late(const Args& a, const RoleCtx& ctx) {
+        BnStatsRole::collect_deferred<T>(a, ctx);
     }
 };
 

@@ -37,6 +37,29 @@ fused_kernel(const __grid_constant__ typename RoleA::Args a, const __grid_consta
     }
 }
 
+// Fused pair whose second role has a wait in the middle (the cross-GPU exchange of the
+// batch-norm moments): role B's range runs the first half of its own work (compute and send),
+// then takes over items [split, items) of role A's work, and only then runs its second half
+// (collect), so the wait for the peers is covered by useful work instead of ending the kernel.
+// Role A's range works on items [0, split).
+template <class RoleA, class RoleB, int TA, int TB, int MINB>
+__global__ void __launch_bounds__(TA + TB, MINB)
+fused_share_kernel(const __grid_constant__ typename RoleA::Args a, const __grid_constant__ typename RoleB::Args b,
+                   int smem_off_b, unsigned split, unsigned items) {
+    static_assert(TA % 32 == 0 && TB % 32 == 0, "ranges are whole warps, so the guard never splits a warp");
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int tid = (int)threadIdx.x;
+    if (tid < TA) {
+        RoleCtx ctx{tid, (int)blockIdx.x, (int)gridDim.x, smem};
+        RoleA::template run_range<TA>(a, ctx, 0u, split);
+    } else {
+        RoleCtx ctx{tid - TA, (int)blockIdx.x, (int)gridDim.x, smem + smem_off_b};
+        RoleB::template run_early<TB, 2>(b, ctx);
+        RoleA::template run_range<TB>(a, ctx, split, items);
+        RoleB::template run_late<TB, 2>(b, ctx);
+    }
+}
+
 // Vertical fusion, the reference's `vfuse` presets (tools/llvm-smart-fuser/main.cpp:182-193,
 // include/KernelFusion.h:75-78): every thread range starts at 0, i.e. the SAME threads run
 // body 1 and then body 2, block = max(T1, T2).  Kept as the third column of the comparison

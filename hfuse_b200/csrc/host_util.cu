@@ -1,5 +1,6 @@
 // Host-side utilities of the C ABI: error strings, the tuning table and the
 // seeded byte generator the synthetic workloads are drawn from.
+#include <cstring>
 #include "launch.cuh"
 
 namespace hfuse {
@@ -45,10 +46,17 @@ int hfuse_tune_set(const char* pair, int variant, int blocks_per_sm) {
         if (hfuse_tune_describe(pair, 0, tmp, sizeof tmp) == HFUSE_ERR_UNKNOWN_PAIR) return HFUSE_ERR_UNKNOWN_PAIR;
     }
     std::lock_guard<std::mutex> lk(hfuse::tune_mutex());
-    hfuse::Tune t;
+    hfuse::Tune& t = hfuse::tune_table()[pair];      // a share set through hfuse_tune_set_share stays
     t.variant = variant < 0 ? -1 : variant;
     t.blocks_per_sm = blocks_per_sm;
-    hfuse::tune_table()[pair] = t;
+    return HFUSE_OK;
+}
+
+int hfuse_tune_set_share(const char* pair, int permille) {
+    if (!pair || permille < -1 || permille > 1000) return HFUSE_ERR_BAD_ARG;
+    if (strcmp(pair, "upsample_bnstats_allreduce") != 0) return HFUSE_ERR_UNKNOWN_PAIR;
+    std::lock_guard<std::mutex> lk(hfuse::tune_mutex());
+    hfuse::tune_table()[pair].share_permille = permille;
     return HFUSE_OK;
 }
 

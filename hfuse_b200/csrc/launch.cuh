@@ -60,6 +60,7 @@ inline int resident_blocks(const void* func, int block, size_t smem) {
 struct Tune {
     int variant = -1;         // -1: the pair's compiled default
     int blocks_per_sm = 0;    // 0: as many as are resident
+    int share_permille = -1;  // -1: the pair's compiled default (pairs launched through launch_pair_share)
 };
 
 inline std::map<std::string, Tune>& tune_table() {
@@ -109,6 +110,32 @@ int launch_pair(typename RA::Args a, typename RB::Args b, int blocks_per_sm, cud
     if (int rc = RA::plan(a, TA, grid)) return rc;
     if (int rc = RB::plan(b, TB, grid)) return rc;
     kern<<<grid, TA + TB, smem, s>>>(a, b, smem_a);
+    return check_launch();
+}
+
+// ---- two roles side by side, the second one taking over a share of the first one's items -----
+// share_permille of role A's items (rounded down to whole rows) go to role B's thread range.
+template <class RA, class RB, int TA, int TB, int MINB>
+int launch_pair_share(typename RA::Args a, typename RB::Args b, int blocks_per_sm, int share_permille, cudaStream_t s) {
+    DeviceFacts f;
+    if (int rc = device_facts(f)) return rc;
+    auto kern = fused_share_kernel<RA, RB, TA, TB, MINB>;
+    if (int rc = RA::plan(a, TA, f.sms * MINB)) return rc;
+    if (int rc = RB::plan(b, TB, f.sms * MINB)) return rc;
+    const int smem_a = (RA::smem_bytes(a, TA) + 15) & ~15;
+    const size_t smem = (size_t)smem_a + (size_t)RB::smem_bytes(b, TB);
+    const int bps = blocks_per_sm > 0 ? blocks_per_sm : resident_blocks((const void*)kern, TA + TB, smem);
+    const int grid = f.sms * bps;
+    if (int rc = RA::plan(a, TA, grid)) return rc;
+    if (int rc = RB::plan(b, TB, grid)) return rc;
+    unsigned items = 1, split = 1;          // scalar path: role A keeps everything
+    if (a.mode != 0) {
+        items = RA::vec_items(a);
+        const unsigned row = RA::vec_row_items(a);
+        const unsigned long long given = (unsigned long long)items * (unsigned)share_permille / 1000ull;
+        split = items - (unsigned)(given / row * row);
+    }
+    kern<<<grid, TA + TB, smem, s>>>(a, b, smem_a, split, items);
     return check_launch();
 }
 

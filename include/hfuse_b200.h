@@ -300,6 +300,10 @@ HFUSE_API int hfuse_hash_batch(int kind, const uint8_t* header, const void* dag,
  * ------------------------------------------------------------------------------------- */
 HFUSE_API int hfuse_tune_set(const char* pair, int variant, int blocks_per_sm);
 HFUSE_API int hfuse_tune_describe(const char* pair, int variant, char* buf, size_t buflen);
+/* "upsample_bnstats_allreduce" only: per mille (0..1000, -1 = compiled default) of the upsample's
+ * items that the statistics thread range takes over between sending its moments to the peers and
+ * waiting for theirs.  Any other name: HFUSE_ERR_UNKNOWN_PAIR. */
+HFUSE_API int hfuse_tune_set_share(const char* pair, int permille);
 
 /* Host utility: xoshiro256** byte stream (state = four splitmix64 outputs of `seed`,
  * little-endian u64 words) — the generator the synthetic DAG and headers are drawn from. */

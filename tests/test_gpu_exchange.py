@@ -42,13 +42,51 @@ def test_world_of_one_matches_plain_kernels_over_many_calls(dev):
         ex.close()
 
 
+def test_statistics_range_takes_over_any_share_of_the_upsample(dev):
+    """The fused exchange kernel hands per-mille shares of the upsample to the statistics thread
+    range (after it has sent its moments).  Every share, every thread split and all three upsample
+    paths (x2 strips, 4-wide, scalar) must give the bits of the plain kernels."""
+    from hfuse_b200 import _lib
+    from hfuse_b200.exchange import BnExchange
+    g = torch.Generator().manual_seed(77)
+    x = 0.5 + 2.0 * torch.randn(6, 40, 9, 12, generator=g)
+    mr, sr = dl.bnstats_f64(x, 1e-5)
+    cases = [((3, 5, 12, 16), dict(scale_factor=2)),          # x2 strip path
+             ((2, 3, 7, 8), dict(scale_factor=2)),
+             ((2, 3, 9, 10), dict(size=(13, 24))),            # 4-wide path
+             ((2, 3, 9, 10), dict(size=(11, 15)))]            # scalar path
+    ex = BnExchange(40)
+    try:
+        for variant in (15, 3, 0, 11):
+            for share in (0, 1, 250, 500, 999, 1000):
+                _lib.tune_set("upsample_bnstats_allreduce", variant, 0)
+                _lib.tune_set_share("upsample_bnstats_allreduce", share)
+                for shape, kw in cases:
+                    up = torch.rand(*shape, generator=g)
+                    a, b = ops.Upsample(up.to(dev), **kw), ops.BnStats(x.to(dev), 1e-5)
+                    ex.run_pair(a, b)
+                    oh, ow = a.out.shape[-2:]
+                    assert np.array_equal(a.out.cpu().numpy(), dl.upsample_numpy(up.numpy(), oh, ow)), (variant, share, shape)
+                    np.testing.assert_allclose(b.mean.cpu().double().numpy(), mr.numpy(), rtol=1e-5)
+                    np.testing.assert_allclose(b.invstd.cpu().double().numpy(), sr.numpy(), rtol=1e-5)
+        assert not ex.timed_out()
+    finally:
+        _lib.tune_set("upsample_bnstats_allreduce", -1, 0)
+        _lib.tune_set_share("upsample_bnstats_allreduce", -1)
+        ex.close()
+    with pytest.raises(_lib.HfuseError):
+        _lib.tune_set_share("upsample_bnstats", 100)          # only the exchange pair has a share
+    with pytest.raises(_lib.HfuseError):
+        _lib.tune_set_share("upsample_bnstats_allreduce", 1001)
+
+
 def _rank_main(rank, world, port, ret):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     torch.cuda.set_device(rank)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from hfuse_b200 import sharding
+        from hfuse_b200 import _lib, sharding
         from hfuse_b200.exchange import BnExchange
         dev = torch.device("cuda", rank)
         ex = BnExchange(24)
@@ -60,6 +98,7 @@ def _rank_main(rank, world, port, ret):
             up = torch.rand(2, 3, 8, 8, generator=g)
             a, b = ops.Upsample(up.to(dev), scale_factor=2), ops.BnStats(mine, 1e-5)
             if it % 2:
+                _lib.tune_set_share("upsample_bnstats_allreduce", (0, 400, 1000)[it % 3])
                 ex.run_pair(a, b)
                 ok &= np.array_equal(a.out.cpu().numpy(), dl.upsample_numpy(up.numpy(), 16, 16))
             else:
