@@ -782,13 +782,19 @@ NCU_TRAFFIC_BYTES = 101_030_656
 
 def run_only(args, torch, ops, crypto, workloads, dev):
     """One kernel or pair on its benchmark configuration, for profiling:
-    --only cfg0|cfg1|cfg2|cfg3|cfg4 --mode fused|b2b|a|b [--graph]"""
+    --only cfg0|cfg1|cfg2|cfg3|cfg4 --mode fused|b2b|a|b [--graph]; cfg1 also takes --mode xchg, the
+    exchange pair (send, share of the upsample, collect) over a world of one."""
     cfg = int(args.only[-1])
     barrier = lambda: None
     if cfg <= 2:
         name, sets, nbytes = build_dl_sets(torch, ops, workloads, cfg, dev, 2)
-        fn = {"fused": lambda i: ops.run_pair(*sets[i % 2]), "b2b": lambda i: ops.run_back_to_back(*sets[i % 2]),
-              "a": lambda i: ops.run(sets[i % 2][0]), "b": lambda i: ops.run(sets[i % 2][1])}[args.mode]
+        if args.mode == "xchg":
+            from hfuse_b200.exchange import BnExchange
+            ex = BnExchange(sets[0][1].x.shape[1])
+            fn = lambda i: ex.run_pair(*sets[i % 2])
+        else:
+            fn = {"fused": lambda i: ops.run_pair(*sets[i % 2]), "b2b": lambda i: ops.run_back_to_back(*sets[i % 2]),
+                  "a": lambda i: ops.run(sets[i % 2][0]), "b": lambda i: ops.run(sets[i % 2][1])}[args.mode]
         if args.graph:
             ms = graph_region(torch, fn, 2, args.steps, args.warmup)
         else:
@@ -974,7 +980,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default="")
-    ap.add_argument("--mode", default="fused", choices=["fused", "b2b", "a", "b"])
+    ap.add_argument("--mode", default="fused", choices=["fused", "b2b", "a", "b", "xchg"])
     ap.add_argument("--count", type=int, default=1 << 24, help="nonces per step with --only cfg3|cfg4")
     ap.add_argument("--dag-items", type=int, default=8_388_608)
     ap.add_argument("--no-extras", action="store_true")
