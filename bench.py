@@ -555,6 +555,16 @@ def run_ours(args):
     cdst = [torch.empty(half, dtype=torch.float32, device=dev) for _ in range(NSETS)]
     t_copy = graph_region(torch, lambda i: cdst[i % NSETS].copy_(csrc[i % NSETS]), NSETS, 120, 3)
     del csrc, cdst
+    # and a bare load/store kernel with the fused pair's own mix: 51,380,224 B read (both inputs), 102,762,496 B written
+    rd, wr = 51_380_224, 102_762_496
+    psrc = [torch.empty(rd // 4, dtype=torch.float32, device=dev).normal_() for _ in range(NSETS)]
+    pdst = [torch.empty(wr // 4, dtype=torch.float32, device=dev) for _ in range(NSETS)]
+
+    def probe(i):
+        _lib.check(_lib.lib().hfuse_hbm_probe(psrc[i % NSETS].data_ptr(), rd, pdst[i % NSETS].data_ptr(), wr,
+                                              torch.cuda.current_stream().cuda_stream), "hfuse_hbm_probe")
+    t_mix = graph_region(torch, probe, NSETS, 120, 3)
+    del psrc, pdst
 
     # ---- end to end through the C ABI with host buffers (pinned), copies inside the timed region
     w = workloads.config1()
@@ -641,7 +651,8 @@ def run_ours(args):
                      "frac": round(nbytes / t_kernel / 1e6 / peak, 4), "traffic": NCU_TRAFFIC_BYTES,
                      "peak_kind": peak_kind, "kernel": "fused_kernel<UpsampleRole,BnStatsRole>",
                      "kernel_us": round(t_kernel * 1e3, 2),
-                     "same_bytes_memcpy_d2d_us": round(t_copy * 1e3, 2)},
+                     "same_bytes_memcpy_d2d_us": round(t_copy * 1e3, 2),
+                     "same_read_write_mix_bare_kernel_us": round(t_mix * 1e3, 2)},
         "clocks": clocks,
     }
     if rank == 0 and world == 1:

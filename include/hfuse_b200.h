@@ -317,6 +317,12 @@ HFUSE_API void hfuse_xoshiro256ss_fill(uint64_t seed, void* host_dst, size_t nby
  * caller times the launch and divides.  `sink` is 4 device bytes that are never written. */
 HFUSE_API int hfuse_int32_probe(int mix, uint32_t iters, uint32_t* sink, uint64_t* lane_ops, hfuse_stream_t stream);
 
+/* Measurement utility (no counterpart in the reference): one launch that reads read_bytes from src
+ * (16-byte loads) and writes write_bytes to dst (32-byte streaming stores) and does nothing else:
+ * the memory-traffic mix of a kernel, without the kernel.  read_bytes / 16 <= write_bytes / 32;
+ * dst 32-byte aligned, src 16-byte aligned, sizes multiples of 32 and 16. */
+HFUSE_API int hfuse_hbm_probe(const void* src, size_t read_bytes, void* dst, size_t write_bytes, hfuse_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

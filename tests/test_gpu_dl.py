@@ -234,3 +234,19 @@ def test_outputs_that_are_only_16_byte_aligned_take_the_narrow_store_paths(dev):
     ops.run(op)
     vr, ir = dl.maxpool_torch(p, 2, 2, 2, 2, 0, 0, 1, 1)
     assert torch.equal(op.out.cpu(), vr) and torch.equal(idx.cpu(), ir)
+
+
+def test_hbm_probe_copies_what_it_reads_and_rejects_bad_arguments(dev):
+    from hfuse_b200 import _lib
+    L = _lib.lib()
+    src = torch.randn(4 * 1000, device=dev)
+    dst = torch.zeros(8 * 3000, device=dev)
+    assert L.hfuse_hbm_probe(src.data_ptr(), src.numel() * 4, dst.data_ptr(), dst.numel() * 4, None) == 0
+    got = dst.cpu().view(3000, 2, 4)
+    want = src.cpu().view(1000, 4)
+    assert torch.equal(got[:1000, 0], want) and torch.equal(got[:1000, 1], want)
+    assert torch.equal(got[1000:], torch.tensor([1., 2., 3., 4.]).expand(2000, 2, 4))
+    assert L.hfuse_hbm_probe(None, 0, dst.data_ptr(), dst.numel() * 4, None) == 0             # write only
+    assert L.hfuse_hbm_probe(src.data_ptr(), 16, dst.data_ptr(), 0, None) == -1
+    assert L.hfuse_hbm_probe(src.data_ptr(), 64, dst.data_ptr(), 64, None) == -1              # more loads than stores
+    assert L.hfuse_hbm_probe(src.data_ptr(), 16, dst.data_ptr() + 16, 32, None) == -2         # alignment
