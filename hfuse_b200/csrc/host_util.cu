@@ -60,6 +60,15 @@ int hfuse_tune_set_share(const char* pair, int permille) {
     return HFUSE_OK;
 }
 
+int hfuse_shard_range(uint64_t total, int rank, int world, uint64_t* offset, uint64_t* length) {
+    if (world <= 0 || rank < 0 || rank >= world || !offset || !length) return HFUSE_ERR_BAD_ARG;
+    const uint64_t base = total / (uint64_t)world, extra = total % (uint64_t)world;
+    const uint64_t r = (uint64_t)rank;
+    *length = base + (r < extra ? 1 : 0);
+    *offset = r * base + (r < extra ? r : extra);
+    return HFUSE_OK;
+}
+
 static inline uint64_t rotl(uint64_t x, int k) { return (x << k) | (x >> (64 - k)); }
 
 void hfuse_xoshiro256ss_fill(uint64_t seed, void* host_dst, size_t nbytes) {

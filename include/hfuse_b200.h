@@ -305,6 +305,12 @@ HFUSE_API int hfuse_tune_describe(const char* pair, int variant, char* buf, size
  * waiting for theirs.  Any other name: HFUSE_ERR_UNKNOWN_PAIR. */
 HFUSE_API int hfuse_tune_set_share(const char* pair, int permille);
 
+/* Host utility (no counterpart in the reference, which is single-GPU): the share of `total` batch
+ * items or nonces that rank `rank` of `world` works on, one process per GPU.  Contiguous and
+ * balanced: the first total % world ranks get one item more; a length may be zero.  A sharded
+ * nonce sweep is hfuse_*_search(start + offset, length) on every rank. */
+HFUSE_API int hfuse_shard_range(uint64_t total, int rank, int world, uint64_t* offset, uint64_t* length);
+
 /* Host utility: xoshiro256** byte stream (state = four splitmix64 outputs of `seed`,
  * little-endian u64 words) — the generator the synthetic DAG and headers are drawn from. */
 HFUSE_API void hfuse_xoshiro256ss_fill(uint64_t seed, void* host_dst, size_t nbytes);

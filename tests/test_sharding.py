@@ -25,6 +25,22 @@ def test_shard_range_covers_everything_once():
         sharding.shard_range(4, 2, 2)
 
 
+def test_c_abi_shard_range_agrees_with_the_python_split():
+    """hfuse_shard_range is host arithmetic: it runs without a GPU."""
+    import ctypes
+    from hfuse_b200 import _lib
+    L = _lib.lib()
+    off, n = ctypes.c_uint64(), ctypes.c_uint64()
+    for total in (0, 1, 7, 16, 2 ** 32, 2 ** 30 + 3, 2 ** 63 + 5):
+        for world in (1, 2, 3, 8):
+            for r in range(world):
+                assert L.hfuse_shard_range(total, r, world, ctypes.byref(off), ctypes.byref(n)) == 0
+                assert (off.value, n.value) == sharding.shard_range(total, r, world)
+    assert L.hfuse_shard_range(4, 2, 2, ctypes.byref(off), ctypes.byref(n)) == -1
+    assert L.hfuse_shard_range(4, 0, 0, ctypes.byref(off), ctypes.byref(n)) == -1
+    assert L.hfuse_shard_range(4, 0, 1, None, ctypes.byref(n)) == -1
+
+
 def test_nonce_shards_keep_64_bit_counts():
     # a full 32-bit sweep starting near the top of the space
     start, count = 0xFFFFFF00, 1 << 32
