@@ -483,13 +483,13 @@ def run_ours(args):
     # Warm-up, then the timed region.  The K steps are replayed from a CUDA graph that holds
     # GRAPH_STEPS consecutive steps (kernel launches, and with N > 1 the all-reduce and the
     # finalize kernel on the side stream), so the host only issues one graph launch per
-    # GRAPH_STEPS steps; K % GRAPH_STEPS left-over steps are launched directly.
+    # GRAPH_STEPS steps; the K % GRAPH_STEPS left-over steps are replayed from a shorter graph of their own.
     for i in range(max(args.warmup, NSETS)):
         step(i)
     drain()
     torch.cuda.synchronize()
     GRAPH_STEPS = 4 * NSETS
-    graph = None
+    graph = tail_graph = None
     if not args.no_graph and args.steps >= GRAPH_STEPS:
         try:
             for k in range(NSETS):
@@ -503,9 +503,19 @@ def run_ours(args):
             torch.cuda.synchronize()
             for k in range(NSETS):
                 done[k] = None          # events recorded during capture must not be waited on outside
+            if args.steps % GRAPH_STEPS:   # the left-over steps get a (shorter) graph of their own
+                tail_graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(tail_graph, capture_error_mode="thread_local"):
+                    for i in range(args.steps % GRAPH_STEPS):
+                        step(i)
+                    drain()
+                tail_graph.replay()
+                torch.cuda.synchronize()
+                for k in range(NSETS):
+                    done[k] = None
         except Exception as exc:          # capture unsupported here: time direct launches instead
             sys.stderr.write(f"CUDA graph capture failed ({exc!r}); timing direct launches\n")
-            graph = None
+            graph = tail_graph = None
             torch.cuda.synchronize()
             for k in range(NSETS):
                 done[k] = None
@@ -516,8 +526,8 @@ def run_ours(args):
     if graph is not None:
         for _ in range(args.steps // GRAPH_STEPS):
             graph.replay()
-        for i in range(args.steps % GRAPH_STEPS):
-            step(i)
+        if tail_graph is not None:
+            tail_graph.replay()
     else:
         for i in range(args.steps):
             step(i)
