@@ -519,8 +519,8 @@ def run_ours(args):
             torch.cuda.synchronize()
             for k in range(NSETS):
                 done[k] = None
+    sampler.start()       # before the barrier: starting it takes a variable time on every rank
     barrier()
-    sampler.start()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s.record()
     if graph is not None:
