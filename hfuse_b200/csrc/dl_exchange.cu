@@ -125,9 +125,11 @@ int hfuse_upsample_bnstats_allreduce_f32(HFUSE_UPSAMPLE_PARAMS(a_), HFUSE_BNSTAT
     // Its own tuning entry.  The statistics range sends its moments, then works through a share of
     // the upsample and only then waits for the peers, so the best split gives that range more
     // threads than the single-GPU pair does (it should finish its own work early).
-    return dispatch_pair_share<UpsampleRole, BnStatsXchgRole>("upsample_bnstats_allreduce",
-                                                              kDefaultPair_upsample_bnstats_allreduce,
-                                                              kDefaultShare_upsample_bnstats_allreduce, a, b, S_(stream));
+    const bool wide = ex->world > 2;      // measured at 2 and at 8 ranks (bench.py --tune-share)
+    return dispatch_pair_share<UpsampleRole, BnStatsXchgRole>(
+        "upsample_bnstats_allreduce",
+        wide ? kDefaultPair_upsample_bnstats_allreduce_wide : kDefaultPair_upsample_bnstats_allreduce,
+        wide ? kDefaultShare_upsample_bnstats_allreduce_wide : kDefaultShare_upsample_bnstats_allreduce, a, b, S_(stream));
 }
 
 }  // extern "C"
