@@ -46,6 +46,9 @@ CFG1_BYTES = 154_142_720
 CFG0_BYTES = 218_365_952
 CFG2_BYTES = 324_011_008
 ETHASH_BYTES_PER_HASH = 8192
+# both arms (this library, and --impl reference) report under the same names
+METRIC = "fused upsample_bilinear2d + batch_norm_collect_statistics pair, HBM throughput"
+WORKLOAD = "config 1: bilinear x2 upsample [16,128,56,56] + batch-norm statistics [32,256,28,28], fp32, per GPU"
 # 32-bit operations per nonce, counted from the specifications.
 # SPEC_OPS: every add, xor, rotate and boolean separate (no three-input adds, no merged logic):
 #   BLAKE-256   14 rounds x 8 G x (6 add + 6 xor + 4 rotate)
@@ -371,11 +374,11 @@ def run_reference(args):
     ms, cores = cpu_pair_cfg1(torch, steps, min(args.warmup, 3))
     val = CFG1_BYTES / ms / 1e6
     line = {
-        "impl": "reference", "metric": "fused upsample_bilinear2d + batch_norm_collect_statistics pair, HBM-equivalent throughput",
+        "impl": "reference", "metric": METRIC,
         "value": round(val, 3), "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 3),
         "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "config 1: bilinear x2 upsample [16,128,56,56] + batch-norm statistics [32,256,28,28], fp32"},
+        "config": {"workload": WORKLOAD},
         "cpu_baseline": {"value": round(val, 3), "unit": "GB/s", "cores": cores, "kind": "port",
                          "sample": f"{steps} full passes of configuration 1 with PyTorch CPU operators "
                                    "(F.interpolate bilinear + var_mean), all host threads"},
@@ -644,12 +647,11 @@ def run_ours(args):
     d2h = h_out.numel() * 4 + h_stats[0].numel() * 4
 
     line = {
-        "metric": "fused upsample_bilinear2d + batch_norm_collect_statistics pair, HBM throughput",
+        "metric": METRIC,
         "value": round(world * nbytes * args.steps / ms / 1e6, 1), "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 5),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "config 1: bilinear x2 upsample [16,128,56,56] + batch-norm statistics [32,256,28,28], "
-                               "fp32, per GPU", "l2": f"steps rotate over {NSETS} independent buffer sets "
+        "config": {"workload": WORKLOAD, "l2": f"steps rotate over {NSETS} independent buffer sets "
                                f"({NSETS * nbytes >> 20} MiB in total, L2 is 126 MB)",
                    "launch": ("CUDA graph of %d steps, replayed" % GRAPH_STEPS) if graph is not None else "direct launches",
                    "parallelism": f"batch-sharded x{world}", "collective": collective},
