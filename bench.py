@@ -577,6 +577,11 @@ def run_ours(args):
         _lib.check(_lib.lib().hfuse_hbm_probe(psrc[i % NSETS].data_ptr(), rd, pdst[i % NSETS].data_ptr(), wr,
                                               torch.cuda.current_stream().cuda_stream), "hfuse_hbm_probe")
     t_mix = graph_region(torch, probe, NSETS, 120, 3)
+
+    def probe_w(i):     # the same kernel writing only: what this memory sustains for pure stores
+        _lib.check(_lib.lib().hfuse_hbm_probe(None, 0, pdst[i % NSETS].data_ptr(), wr,
+                                              torch.cuda.current_stream().cuda_stream), "hfuse_hbm_probe")
+    t_wr = graph_region(torch, probe_w, NSETS, 120, 3)
     del psrc, pdst
 
     # ---- end to end through the C ABI with host buffers (pinned), copies inside the timed region
@@ -664,7 +669,8 @@ def run_ours(args):
                      "peak_kind": peak_kind, "kernel": "fused_kernel<UpsampleRole,BnStatsRole>",
                      "kernel_us": round(t_kernel * 1e3, 2),
                      "same_bytes_memcpy_d2d_us": round(t_copy * 1e3, 2),
-                     "same_read_write_mix_bare_kernel_us": round(t_mix * 1e3, 2)},
+                     "same_read_write_mix_bare_kernel_us": round(t_mix * 1e3, 2),
+                     "write_only_bare_kernel_gbs": round(wr / t_wr / 1e6, 1)},
         "clocks": clocks,
     }
     if rank == 0 and world == 1:
