@@ -80,6 +80,33 @@ def test_statistics_range_takes_over_any_share_of_the_upsample(dev):
         _lib.tune_set_share("upsample_bnstats_allreduce", 1001)
 
 
+def test_full_size_configuration_1_through_the_exchange_pair(dev):
+    """Benchmark configuration 1 (256 channels: one channel per block, the deferred collect) through
+    the exchange entry point, with the compiled defaults and with the many-rank defaults."""
+    from hfuse_b200 import _lib, workloads
+    from hfuse_b200.exchange import BnExchange
+    w = workloads.config1()
+    ref = dl.upsample_numpy(w["up"].numpy(), 112, 112)
+    mr, sr = dl.bnstats_f64(w["bn"], w["eps"])
+    ex = BnExchange(256)
+    try:
+        for variant, share in ((-1, -1), (21, 400), (15, 0)):
+            _lib.tune_set("upsample_bnstats_allreduce", variant, 0)
+            _lib.tune_set_share("upsample_bnstats_allreduce", share)
+            for _ in range(3):
+                a = ops.Upsample(w["up"].to(dev), scale_factor=2)
+                b = ops.BnStats(w["bn"].to(dev), w["eps"])
+                ex.run_pair(a, b)
+                assert np.array_equal(a.out.cpu().numpy(), ref)
+                np.testing.assert_allclose(b.mean.cpu().double().numpy(), mr.numpy(), rtol=1e-5)
+                np.testing.assert_allclose(b.invstd.cpu().double().numpy(), sr.numpy(), rtol=1e-5)
+        assert not ex.timed_out()
+    finally:
+        _lib.tune_set("upsample_bnstats_allreduce", -1, 0)
+        _lib.tune_set_share("upsample_bnstats_allreduce", -1)
+        ex.close()
+
+
 def _rank_main(rank, world, port, ret):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
