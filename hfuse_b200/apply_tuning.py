@@ -3,6 +3,9 @@
     python bench.py --tune > tune.json          (on a B200)
     python -m hfuse_b200.apply_tuning tune.json (anywhere; then rebuild)
 
+    torchrun --nproc-per-node N bench.py --gpus N --tune-share > share.json   (on N B200s)
+    python -m hfuse_b200.apply_tuning --share share.json
+
 The reference picks the split and register cap of each pair by rebuilding and
 profiling every candidate (scripts/profile_and_collect_data.py:40-57); here all
 candidates are compiled in, the sweep runs once, and only the default index per
@@ -39,5 +42,25 @@ def apply(path: str) -> None:
         print("updated", p)
 
 
+def apply_share(path: str) -> None:
+    """Result of `torchrun ... bench.py --gpus N --tune-share`: the thread split and the upsample share
+    of the exchange pair, for two ranks (N <= 2) or for more (the `_wide` defaults)."""
+    with open(path) as f:
+        text = f.read()
+    res = json.loads(text[text.index("{"):])
+    suffix = "_wide" if int(res["n_gpus"]) > 2 else ""
+    p = os.path.join(CSRC, "dl_tuned.inc")
+    src = open(p).read()
+    for key, val in ((f"kDefaultPair_upsample_bnstats_allreduce{suffix}", res["best"]["index"]),
+                     (f"kDefaultShare_upsample_bnstats_allreduce{suffix}", res["best"]["share_permille"])):
+        src, n = re.subn(rf"({key} = )\d+;", rf"\g<1>{int(val)};", src)
+        assert n == 1, key
+    open(p, "w").write(src)
+    print("updated", p)
+
+
 if __name__ == "__main__":
-    apply(sys.argv[1])
+    if sys.argv[1] == "--share":
+        apply_share(sys.argv[2])
+    else:
+        apply(sys.argv[1])
