@@ -811,12 +811,22 @@ NCU_TRAFFIC_BYTES = 101_030_656
 
 def run_only(args, torch, ops, crypto, workloads, dev):
     """One kernel or pair on its benchmark configuration, for profiling:
-    --only cfg0|cfg1|cfg2|cfg3|cfg4 --mode fused|b2b|a|b [--graph]; cfg1 also takes --mode xchg, the
+    --only cfg0|cfg1|cfg2|cfg3|cfg4|histc_maxpool|histc_upsample|histc_bnstats --mode fused|b2b|a|b [--graph]; cfg1 also takes --mode xchg, the
     exchange pair (send, share of the upsample, collect) over a world of one."""
-    cfg = int(args.only[-1])
     barrier = lambda: None
+    hist_pair = args.only.startswith("histc_")
+    cfg = 2 if hist_pair else int(args.only[-1])
     if cfg <= 2:
-        name, sets, nbytes = build_dl_sets(torch, ops, workloads, cfg, dev, 2)
+        if hist_pair:       # the three histc pairs named besides configuration 2: histc_maxpool|upsample|bnstats
+            w0, w1, w2 = workloads.config0(), workloads.config1(), workloads.config2()
+            name, sets = args.only, []
+            for _ in range(2):
+                other = {"histc_maxpool": lambda: ops.MaxPool(w0["pool"].to(dev), **w0["maxpool"]),
+                         "histc_upsample": lambda: ops.Upsample(w1["up"].to(dev), scale_factor=2),
+                         "histc_bnstats": lambda: ops.BnStats(w1["bn"].to(dev), w1["eps"])}[args.only]()
+                sets.append((ops.Histc(w2["hist"].to(dev), w2["bins"], w2["lo"], w2["hi"]), other))
+        else:
+            name, sets, nbytes = build_dl_sets(torch, ops, workloads, cfg, dev, 2)
         if args.mode == "xchg":
             from hfuse_b200.exchange import BnExchange
             ex = BnExchange(sets[0][1].x.shape[1])
