@@ -353,6 +353,8 @@ struct UpsampleRole {
         return a.mode == 2 ? (unsigned)a.N * a.C * ((unsigned)a.H + 1) * ((unsigned)a.W >> 2)
                            : (unsigned)a.N * a.C * (unsigned)a.outH * ((unsigned)a.outW >> 2);
     }
+    // only the vector paths can hand part of their items to another thread range
+    static __host__ __device__ __forceinline__ bool splittable(const Args& a) { return a.mode != 0; }
     // A range of items handed to another thread range must start on a row boundary (the x2
     // path reads its left and right neighbours' columns from the adjacent lanes).
     static __host__ __device__ __forceinline__ unsigned vec_row_items(const Args& a) {

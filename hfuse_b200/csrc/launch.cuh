@@ -129,7 +129,7 @@ int launch_pair_share(typename RA::Args a, typename RB::Args b, int blocks_per_s
     if (int rc = RA::plan(a, TA, grid)) return rc;
     if (int rc = RB::plan(b, TB, grid)) return rc;
     unsigned items = 1, split = 1;          // scalar path: role A keeps everything
-    if (a.mode != 0) {
+    if (RA::splittable(a)) {
         items = RA::vec_items(a);
         const unsigned row = RA::vec_row_items(a);
         const unsigned long long given = (unsigned long long)items * (unsigned)share_permille / 1000ull;
