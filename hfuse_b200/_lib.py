@@ -61,7 +61,8 @@ def exported_symbols() -> list[str]:
     names = list(DL_SOLO.values()) + [f"hfuse_{p}_f32" for p in DL_PAIRS]
     names += list(CRYPTO_SOLO.values()) + [f"hfuse_{p}_search" for p in CRYPTO_PAIRS]
     names += ["hfuse_exchange_create", "hfuse_exchange_local_handle", "hfuse_exchange_connect",
-              "hfuse_exchange_status", "hfuse_exchange_destroy", "hfuse_bnstats_allreduce_f32",
+              "hfuse_exchange_status", "hfuse_exchange_destroy", "hfuse_exchange_local_pointer",
+              "hfuse_exchange_connect_pointers", "hfuse_exchange_set_timeout", "hfuse_bnstats_allreduce_f32",
               "hfuse_upsample_bnstats_allreduce_f32"]
     names += ["hfuse_ethash_make_cache", "hfuse_ethash_generate_dag"]
     names += ["hfuse_maxpool2d_backward_f32", "hfuse_bn_backward_f32", "hfuse_maxpool_backward_bn_backward_f32"]
@@ -112,6 +113,10 @@ def lib() -> C.CDLL:
     L.hfuse_exchange_local_handle.restype, L.hfuse_exchange_local_handle.argtypes = _i, [_p, C.c_char_p]
     L.hfuse_exchange_connect.restype, L.hfuse_exchange_connect.argtypes = _i, [_p, C.c_char_p]
     L.hfuse_exchange_status.restype, L.hfuse_exchange_status.argtypes = _i, [_p, C.POINTER(_i)]
+    L.hfuse_exchange_local_pointer.restype, L.hfuse_exchange_local_pointer.argtypes = _i, [_p, C.POINTER(C.c_void_p)]
+    L.hfuse_exchange_connect_pointers.restype = _i
+    L.hfuse_exchange_connect_pointers.argtypes = [_p, C.POINTER(C.c_void_p)]
+    L.hfuse_exchange_set_timeout.restype, L.hfuse_exchange_set_timeout.argtypes = _i, [_p, _u64]
     L.hfuse_exchange_destroy.restype, L.hfuse_exchange_destroy.argtypes = _i, [_p]
     L.hfuse_bnstats_allreduce_f32.restype, L.hfuse_bnstats_allreduce_f32.argtypes = _i, BNSTATS + [_p, _p]
     L.hfuse_upsample_bnstats_allreduce_f32.restype = _i

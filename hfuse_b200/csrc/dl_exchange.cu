@@ -14,12 +14,11 @@ struct hfuse_exchange {
     bool opened[hfuse::kXchgMaxRanks] = {};
     unsigned uses[hfuse::kXchgSlots] = {};
     unsigned long long calls = 0;
+    unsigned long long timeout_ns = 5ull * 1000 * 1000 * 1000;   // 5 s per exchange wait unless changed
     bool connected = false;
 };
 
 namespace {
-
-constexpr unsigned long long kWaitTimeoutNs = 5ull * 1000 * 1000 * 1000;   // 5 s per exchange wait
 
 int next_use(hfuse_exchange* ex, int C, BnXchg& x) {
     if (!ex || !ex->connected) return HFUSE_ERR_BAD_ARG;
@@ -31,7 +30,7 @@ int next_use(hfuse_exchange* ex, int C, BnXchg& x) {
     x.rank = ex->rank;
     x.slot = slot;
     x.epoch = ex->uses[slot];
-    x.timeout_ns = kWaitTimeoutNs;
+    x.timeout_ns = ex->timeout_ns;
     for (int r = 0; r < hfuse::kXchgMaxRanks; ++r) x.peer[r] = ex->peer[r];
     return HFUSE_OK;
 }
@@ -84,6 +83,29 @@ int hfuse_exchange_connect(hfuse_exchange* ex, const uint8_t* handles) {
         ex->opened[r] = true;
     }
     ex->connected = true;
+    return HFUSE_OK;
+}
+
+int hfuse_exchange_local_pointer(hfuse_exchange* ex, void** buffer) {
+    if (!ex || !buffer) return HFUSE_ERR_BAD_ARG;
+    *buffer = ex->local;
+    return HFUSE_OK;
+}
+
+int hfuse_exchange_connect_pointers(hfuse_exchange* ex, void* const* buffers) {
+    if (!ex || (!buffers && ex->world > 1)) return HFUSE_ERR_BAD_ARG;
+    for (int r = 0; r < ex->world; ++r) {
+        if (r == ex->rank) continue;
+        if (!buffers[r] || ex->opened[r]) return HFUSE_ERR_BAD_ARG;      // not after an IPC connect
+        ex->peer[r] = static_cast<unsigned char*>(buffers[r]);
+    }
+    ex->connected = true;
+    return HFUSE_OK;
+}
+
+int hfuse_exchange_set_timeout(hfuse_exchange* ex, uint64_t nanoseconds) {
+    if (!ex || nanoseconds == 0) return HFUSE_ERR_BAD_ARG;
+    ex->timeout_ns = nanoseconds;
     return HFUSE_OK;
 }
 

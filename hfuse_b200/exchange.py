@@ -49,6 +49,33 @@ class BnExchange:
         else:
             _lib.check(rc, "hfuse_exchange_create")
 
+    @classmethod
+    def local_ranks(cls, channels: int, devices) -> list["BnExchange"]:
+        """Exchange objects for ONE process that drives several ranks: rank r lives on devices[r]
+        (peer access between different devices must already be enabled).  Connected through raw
+        device pointers, no IPC and no torch.distributed."""
+        L = _lib.lib()
+        world = len(devices)
+        out = []
+        for r, d in enumerate(devices):
+            ex = cls.__new__(cls)
+            ex.world, ex.rank, ex.channels, ex._h = world, r, int(channels), C.c_void_p()
+            with torch.cuda.device(d):
+                _lib.check(L.hfuse_exchange_create(world, r, ex.channels, C.byref(ex._h)), "hfuse_exchange_create")
+            out.append(ex)
+        ptrs = (C.c_void_p * world)()
+        for r, ex in enumerate(out):
+            p = C.c_void_p()
+            _lib.check(L.hfuse_exchange_local_pointer(ex._h, C.byref(p)), "hfuse_exchange_local_pointer")
+            ptrs[r] = p.value
+        for ex in out:
+            _lib.check(L.hfuse_exchange_connect_pointers(ex._h, ptrs), "hfuse_exchange_connect_pointers")
+        return out
+
+    def set_timeout(self, seconds: float) -> None:
+        """Limit of the in-kernel wait for the other ranks (default 5 s)."""
+        _lib.check(_lib.lib().hfuse_exchange_set_timeout(self._h, int(seconds * 1e9)), "hfuse_exchange_set_timeout")
+
     def run(self, bn, stream=None):
         """Standalone statistics kernel with the in-kernel all-reduce."""
         _lib.check(_lib.lib().hfuse_bnstats_allreduce_f32(*bn.c_args(), self._h, _stream_ptr(stream)),

@@ -200,6 +200,13 @@ HFUSE_API int hfuse_exchange_create(int world, int rank, int channels, hfuse_exc
 HFUSE_API int hfuse_exchange_local_handle(hfuse_exchange* ex, uint8_t handle[HFUSE_IPC_HANDLE_BYTES]);
 /* handles: world x HFUSE_IPC_HANDLE_BYTES bytes in rank order (host memory); the own entry is ignored */
 HFUSE_API int hfuse_exchange_connect(hfuse_exchange* ex, const uint8_t* handles);
+/* One process that drives several GPUs connects without IPC: it takes every exchange object's
+ * buffer (hfuse_exchange_local_pointer) and gives each object the list of all of them in rank
+ * order; peer access between the devices must be enabled by the caller.  The own entry is ignored. */
+HFUSE_API int hfuse_exchange_local_pointer(hfuse_exchange* ex, void** buffer);
+HFUSE_API int hfuse_exchange_connect_pointers(hfuse_exchange* ex, void* const* buffers);
+/* limit of the in-kernel wait for the other ranks' moments (default 5 s), for later calls */
+HFUSE_API int hfuse_exchange_set_timeout(hfuse_exchange* ex, uint64_t nanoseconds);
 HFUSE_API int hfuse_exchange_status(hfuse_exchange* ex, int* timed_out);   /* synchronises the device */
 HFUSE_API int hfuse_exchange_destroy(hfuse_exchange* ex);
 HFUSE_API int hfuse_bnstats_allreduce_f32(HFUSE_BNSTATS_PARAMS(), hfuse_exchange* ex, hfuse_stream_t stream);

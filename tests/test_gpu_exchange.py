@@ -107,6 +107,43 @@ def test_full_size_configuration_1_through_the_exchange_pair(dev):
         ex.close()
 
 
+def test_a_rank_that_never_arrives_ends_the_wait_with_a_status_and_the_late_rank_still_sums(dev):
+    """Two ranks driven by this process on one GPU, launched one after the other.  Rank 0 runs
+    alone: nothing ever writes rank 1's rows, so its bounded wait (20 ms here) runs out, the kernel
+    returns, the status word is raised and the context stays usable.  Rank 1 then runs: rank 0's
+    rows are already in its buffer, so it does not wait and reports the statistics of both batches."""
+    from hfuse_b200.exchange import BnExchange
+    g = torch.Generator().manual_seed(91)
+    x = 0.5 + 2.0 * torch.randn(8, 24, 10, 10, generator=g)
+    mr, sr = dl.bnstats_f64(x, 1e-5)
+    ex0, ex1 = BnExchange.local_ranks(24, [dev, dev])
+    try:
+        for ex in (ex0, ex1):
+            ex.set_timeout(0.02)
+        b0 = ops.BnStats(x[:4].contiguous().to(dev), 1e-5)
+        b1 = ops.BnStats(x[4:].contiguous().to(dev), 1e-5)
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        ex0.run(b0)
+        t1.record()
+        torch.cuda.synchronize()
+        assert ex0.timed_out() and not ex1.timed_out()
+        assert 15.0 < t0.elapsed_time(t1) < 2000.0                       # gave up after the limit, not at once, not never
+        ex1.run(b1)
+        torch.cuda.synchronize()
+        assert not ex1.timed_out()
+        np.testing.assert_allclose(b1.mean.cpu().double().numpy(), mr.numpy(), rtol=1e-5)
+        np.testing.assert_allclose(b1.invstd.cpu().double().numpy(), sr.numpy(), rtol=1e-5)
+        # the device is still usable for ordinary work
+        c = ops.BnStats(x.to(dev), 1e-5)
+        ops.run(c)
+        np.testing.assert_allclose(c.mean.cpu().double().numpy(), mr.numpy(), rtol=1e-5)
+    finally:
+        ex0.close()
+        ex1.close()
+
+
 def _rank_main(rank, world, port, ret):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
