@@ -43,6 +43,18 @@ def test_tuning_table():
     assert _lib.lib().hfuse_tune_set(b"im2col_maxpool", 999, 0) < 0
     _lib.tune_set("im2col_maxpool", 1, 2)
     _lib.tune_set("im2col_maxpool", -1, 0)
+    # the exchange pair has its own entry (same variant list as the DL pairs) and a share knob
+    assert _lib.tune_variants("upsample_bnstats_allreduce") == _lib.tune_variants("upsample_bnstats")
+    L = _lib.lib()
+    assert L.hfuse_tune_set_share(b"upsample_bnstats_allreduce", 250) == 0
+    assert L.hfuse_tune_set_share(b"upsample_bnstats_allreduce", -1) == 0
+    assert L.hfuse_tune_set_share(b"upsample_bnstats_allreduce", 1001) == -1
+    assert L.hfuse_tune_set_share(b"upsample_bnstats", 100) == -7
+    assert L.hfuse_tune_set_share(None, 100) == -1
+    # exchange objects: argument checks that need no device
+    assert L.hfuse_exchange_create(0, 0, 4, None) == -1
+    assert L.hfuse_exchange_set_timeout(None, 1) == -1
+    assert L.hfuse_exchange_connect_pointers(None, None) == -1
 
 
 def test_bad_arguments_are_rejected_before_any_launch():
