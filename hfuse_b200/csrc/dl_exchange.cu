@@ -2,7 +2,8 @@
 // the warp that finishes a channel stores its moments into every rank's exchange buffer with
 // plain 8-byte NVLink stores that carry their own validity tag, then collects every rank's
 // row for that channel and folds them in rank order (dl_roles.cuh, BnXchg).  No collective library call, no second launch; the
-// wait for the other ranks is bounded in time and overlaps the other thread range's work.
+// wait for the other ranks is bounded in time.  In the fused pair the statistics range sends, works through a
+// share of the upsample, and only then collects (fused_share_kernel), so the wait costs nothing.
 // The reference is single-GPU, so none of this has a counterpart there.
 #include "dl_host.cuh"
 
