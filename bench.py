@@ -14,15 +14,20 @@ every benchmark configuration, the fused time, the time of the same two
 kernels launched back to back on one stream, their ratio, and GB/s or GH/s
 with the roofline fraction.
 
-Timing: CUDA events on the launching stream around the whole K-step region,
-barrier + synchronize on both sides, max over ranks.  The steps rotate over
-several independent buffer sets whose combined footprint is several times the
-L2, so no step finds its inputs in cache.
+Timing: the K steps of one pass are replayed from a CUDA graph; the timed region is R
+such passes (R chosen so that the region lasts about a second, at least 50), every pass
+bracketed by CUDA events on the launching stream, barrier + synchronize on both sides of
+the region, every pass's time the max over ranks, the median pass reported (min, max and
+mean beside it).  The steps rotate over several independent buffer sets whose combined
+footprint is several times the L2, so no step finds its inputs in cache.  After the timed
+region the results left in the buffers are compared with the oracle (`parity_ok`).
 
-With N > 1 (one process per GPU under torch.distributed.run) every rank runs
-the full per-GPU configuration on its own batch shard (weak scaling); the
-per-channel batch-norm moments are summed over ranks with an NCCL all-reduce
-that overlaps the next step's kernel, then finalised on the GPU.
+With N > 1 (one process per GPU under torch.distributed.run) every rank runs the full
+per-GPU configuration on its own batch shard (weak scaling); the per-channel batch-norm
+moments are summed over ranks INSIDE the fused kernel over NVLink peer memory
+(`--collective nccl`: with an NCCL all-reduce and a finalize kernel instead).  The line
+then also carries configuration 2 split over the ranks (`dl_sharded`, strong scaling) and
+the nonce-sharded searches (`crypto_sharded`).
 
 `--impl reference` times the CPU restatement of the same pair (PyTorch CPU
 operators on all host cores) instead: the reference ships no CPU or GPU code
@@ -370,12 +375,12 @@ def run_reference(args):
     if rank != 0:
         return
     import torch
-    steps = min(args.steps, 20)
-    ms, cores = cpu_pair_cfg1(torch, steps, min(args.warmup, 3))
+    steps = args.steps
+    ms, cores = cpu_pair_cfg1(torch, steps, args.warmup)
     val = CFG1_BYTES / ms / 1e6
     line = {
         "impl": "reference", "metric": METRIC,
-        "value": round(val, 3), "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 3),
+        "value": round(val, 3), "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD},
@@ -387,6 +392,87 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def bind_near_gpu(local):
+    """Best effort: run this rank on the host cores next to its GPU before any pinned buffer is
+    allocated, so that the end-to-end copies do not cross sockets.  Returns a short description."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(local)
+        allowed = os.sched_getaffinity(0)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (max(allowed) // 64) + 1)
+        ideal = {64 * i + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+        near = sorted(ideal & allowed)
+        if near and set(near) != allowed:
+            os.sched_setaffinity(0, near)
+            return f"bound to {len(near)} of {len(allowed)} allowed cores next to GPU {local}"
+        return f"all {len(allowed)} allowed cores are next to GPU {local}" if near else "no allowed core is next to the GPU"
+    except Exception as exc:       # NVML missing or refused: leave the affinity alone
+        return f"not bound ({type(exc).__name__})"
+
+
+def weak_seed(rank):
+    """Seed of rank's batch shard of the headline workload (rank 0 = the single-GPU workload)."""
+    return 1 + 1000 * rank
+
+
+def check_headline(torch, sets, w, ex, dev, world):
+    """Outside the timed region: the results the timed launches left in every buffer set against
+    the oracle.  Upsample bit-exact with the NumPy restatement of this rank's input; mean / invstd
+    within 1e-5 of float64 statistics over the batches of ALL ranks (their float64 moments summed
+    with an NCCL all-reduce, a path that shares nothing with the in-kernel exchange); and all
+    ranks must hold identical bits."""
+    import numpy as np
+    from oracle import dl
+    out = {"upsample_bit_exact": True, "stats_within_1e-5": True, "ranks_identical": True}
+    ref_up = dl.upsample_numpy(w["up"].numpy(), 112, 112)
+    x = w["bn"].double()
+    n = float(x.numel() // x.shape[1])
+    mom = torch.stack([torch.full((x.shape[1],), n, dtype=torch.float64), x.sum(dim=(0, 2, 3)),
+                       (x * x).sum(dim=(0, 2, 3))], dim=1).to(dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(mom, op=dist.ReduceOp.SUM)
+    mom = mom.cpu()
+    mean = mom[:, 1] / mom[:, 0]
+    var = (mom[:, 2] / mom[:, 0] - mean * mean).clamp_min(0)
+    invstd = 1.0 / torch.sqrt(var + w["eps"])
+    worst = 0.0
+    for a, b in sets:
+        out["upsample_bit_exact"] &= bool(np.array_equal(a.out.cpu().numpy(), ref_up))
+        em = ((b.mean.cpu().double() - mean).abs() / mean.abs()).max().item()
+        es = ((b.invstd.cpu().double() - invstd).abs() / invstd.abs()).max().item()
+        worst = max(worst, em, es)
+    out["stats_within_1e-5"] = bool(worst <= 1e-5)
+    out["stats_worst_rel_err"] = float(f"{worst:.3e}")
+    if world > 1:
+        import torch.distributed as dist
+        bits = torch.cat([torch.cat([b.mean, b.invstd]) for _, b in sets]).view(torch.int32)
+        lo, hi = bits.clone(), bits.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        out["ranks_identical"] = bool(torch.equal(lo, hi))
+        flags = torch.tensor([int(out["upsample_bit_exact"]), int(out["stats_within_1e-5"])], device=dev)
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        out["upsample_bit_exact"], out["stats_within_1e-5"] = bool(flags[0].item()), bool(flags[1].item())
+    timed_out = bool(ex.timed_out()) if ex is not None else False
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([int(timed_out)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        timed_out = bool(t.item())
+    ok = out["upsample_bit_exact"] and out["stats_within_1e-5"] and out["ranks_identical"] and not timed_out
+    return ok, timed_out, out
+
+
+# DRAM bytes (read + write) per launch of the kernel of the timed region, from one ncu capture of
+# an isolated launch (dram__bytes_read.sum + dram__bytes_write.sum).  Both are below the
+# algorithmic 154,142,720 B because about half of the output is still dirty in L2 when an
+# isolated launch ends; the reads (51.7 MB for 51.4 MB of input) show that nothing is read twice.
+NCU_TRAFFIC_BYTES = {"fused_kernel<UpsampleRole,BnStatsRole,512,256,2>": 101_030_656,
+                     "fused_share_kernel<UpsampleRole,BnStatsXchgRole>": 100_900_000}
+
+
 def run_ours(args):
     import torch
     rank, world, local = dist_env()
@@ -395,6 +481,8 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     use_dist = world > 1
+    # rank 0 keeps all host cores: it also times the CPU baseline
+    binding = bind_near_gpu(local) if use_dist and rank != 0 else "affinity left alone"
     if use_dist:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
@@ -405,6 +493,8 @@ def run_ours(args):
     _lib.lib()   # fail loudly if the CUDA library is missing
     peak, peak_kind = measured_peak_gbs()
 
+    if args.im2col_path == "bulk":
+        _lib.tune_option("im2col_store_path", 1)
     if args.only:
         return run_only(args, torch, ops, crypto, workloads, dev)
     if args.tune:
@@ -413,9 +503,12 @@ def run_ours(args):
         return run_study(args, torch, ops, crypto, workloads, dev)
 
     NSETS = 6
-    name, sets, nbytes = build_dl_sets(torch, ops, workloads, 1, dev, NSETS)
-    launches = 0
-    done = [None] * NSETS
+    # weak scaling: every rank holds its own draw of the per-GPU configuration (its batch shard)
+    w = workloads.config1(seed=weak_seed(rank))
+    sets = []
+    for _ in range(NSETS):
+        sets.append((ops.Upsample(w["up"].to(dev), scale_factor=2), ops.BnStats(w["bn"].to(dev), w["eps"])))
+    nbytes = CFG1_BYTES
     collective = "none"
     ex = None
     if use_dist and args.collective == "fused":
@@ -438,128 +531,110 @@ def run_ours(args):
         _lib.tune_set_share("upsample_bnstats_allreduce", args.share_permille)
     if args.tune_share:
         return run_tune_share(args, torch, _lib, ex, sets, NSETS, dev, rank, barrier, use_dist)
+    stream = torch.cuda.Stream(dev)          # everything timed runs (and is captured) on this stream
     if ex is not None:
         collective = "in-kernel sum of the [256,3] f64 moments over NVLink peer stores"
+        kernel_name = "fused_share_kernel<UpsampleRole,BnStatsXchgRole>"
 
         def step(i):
             ex.run_pair(*sets[i % NSETS])
-
-        def drain():
-            pass
         per_step_launches = 1
     elif use_dist:
-        # per-GPU moments -> NCCL all-reduce on a side stream (overlaps the next step) -> finalize
-        collective = "NCCL all-reduce of the [256,3] f64 moments on a side stream + finalize kernel"
-        comm_stream = torch.cuda.Stream(dev)
-        moms = [torch.empty((256, 3), dtype=torch.float64, device=dev) for _ in range(NSETS)]
-        for (a, b), m in zip(sets, moms):
-            b.moments = m
-        stats = [None] * NSETS
+        # per-GPU moments -> NCCL all-reduce -> finalize kernel, all on the timed stream
+        collective = "NCCL all-reduce of the [256,3] f64 moments + finalize kernel"
+        kernel_name = "fused_kernel<UpsampleRole,BnStatsRole,512,256,2>"
+        for a, b in sets:
+            b.moments = torch.empty((256, 3), dtype=torch.float64, device=dev)
 
         def step(i):
-            k = i % NSETS
-            a, b = sets[k]
-            if done[k] is not None:
-                torch.cuda.current_stream().wait_event(done[k])     # buffer set k is free again
+            a, b = sets[i % NSETS]
             ops.run_pair(a, b)
-            ready = torch.cuda.Event()
-            ready.record()
-            with torch.cuda.stream(comm_stream):
-                comm_stream.wait_event(ready)
-                sharding.allreduce_moments(b.moments)
-                stats[k] = ops.bn_finalize(b.moments, b.eps)
-                done[k] = torch.cuda.Event()
-                done[k].record()
-
-        def drain():
-            torch.cuda.current_stream().wait_stream(comm_stream)
-        per_step_launches = 2
+            sharding.allreduce_moments(b.moments)
+            m, s_ = ops.bn_finalize(b.moments, b.eps)
+            b.mean.copy_(m)
+            b.invstd.copy_(s_)
+        per_step_launches = 5
     else:
+        kernel_name = "fused_kernel<UpsampleRole,BnStatsRole,512,256,2>"
+
         def step(i):
             ops.run_pair(*sets[i % NSETS])
-
-        def drain():
-            pass
         per_step_launches = 1
 
-    sampler = ClockSampler(local)
-    # Warm-up, then the timed region.  The K steps are replayed from a CUDA graph that holds
-    # GRAPH_STEPS consecutive steps (kernel launches, and with N > 1 the all-reduce and the
-    # finalize kernel on the side stream), so the host only issues one graph launch per
-    # GRAPH_STEPS steps; the K % GRAPH_STEPS left-over steps are replayed from a shorter graph of their own.
-    for i in range(max(args.warmup, NSETS)):
-        step(i)
-    drain()
-    torch.cuda.synchronize()
-    GRAPH_STEPS = 4 * NSETS
-    graph = tail_graph = None
-    if not args.no_graph and args.steps >= GRAPH_STEPS:
-        try:
-            for k in range(NSETS):
-                done[k] = None
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-                for i in range(GRAPH_STEPS):
-                    step(i)
-                drain()
-            graph.replay()
-            torch.cuda.synchronize()
-            for k in range(NSETS):
-                done[k] = None          # events recorded during capture must not be waited on outside
-            if args.steps % GRAPH_STEPS:   # the left-over steps get a (shorter) graph of their own
-                tail_graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(tail_graph, capture_error_mode="thread_local"):
-                    for i in range(args.steps % GRAPH_STEPS):
-                        step(i)
-                    drain()
-                tail_graph.replay()
-                torch.cuda.synchronize()
-                for k in range(NSETS):
-                    done[k] = None
-        except Exception as exc:          # capture unsupported here: time direct launches instead
-            sys.stderr.write(f"CUDA graph capture failed ({exc!r}); timing direct launches\n")
-            graph = tail_graph = None
-            torch.cuda.synchronize()
-            for k in range(NSETS):
-                done[k] = None
-    sampler.start()       # before the barrier: starting it takes a variable time on every rank
-    barrier()
-    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s.record()
-    if graph is not None:
-        for _ in range(args.steps // GRAPH_STEPS):
-            graph.replay()
-        if tail_graph is not None:
-            tail_graph.replay()
-    else:
-        for i in range(args.steps):
+    # ---- warm-up, capture, timed region ------------------------------------------------------
+    # The K steps of one pass are replayed from CUDA graphs (one graph of up to 240 consecutive
+    # steps, plus a shorter one for what is left), so the host issues a handful of launches per
+    # pass whatever K is.  A pass of K steps lasts well under a millisecond for small K, so the
+    # timed region is R passes, R chosen so that the region lasts about a second (at least 50):
+    # every pass is bracketed by CUDA events on the launching stream, each pass's time is the
+    # maximum over ranks, and the figure reported is the median pass (min, max and mean beside
+    # it).  The clock sampler runs over exactly that region.
+    K = args.steps
+    G = min(K, 240)
+    graphs = []
+    launch_mode = "direct launches"
+    with torch.cuda.stream(stream):
+        for i in range(max(args.warmup, NSETS)):
             step(i)
-    drain()
-    e.record()
+        stream.synchronize()
+        if not args.no_graph:
+            try:
+                for n in ([G] if K % G == 0 else [G, K % G]):
+                    g_ = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g_, stream=stream, capture_error_mode="thread_local"):
+                        for i in range(n):
+                            step(i)
+                    graphs.append(g_)
+                launch_mode = f"CUDA graph of {G} steps, replayed"
+            except Exception as exc:          # capture unsupported here: time direct launches instead
+                sys.stderr.write(f"CUDA graph capture failed ({exc!r}); timing direct launches\n")
+                graphs = []
+                torch.cuda.synchronize()
+
+        def one_pass():
+            if graphs:
+                for _ in range(K // G):
+                    graphs[0].replay()
+                if K % G:
+                    graphs[1].replay()
+            else:
+                for i in range(K):
+                    step(i)
+
+        for _ in range(3):                    # warm replays; the last one sizes the region
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            one_pass()
+            e1.record()
+            e1.synchronize()
+        est = torch.tensor([max(e0.elapsed_time(e1), 1e-3)], dtype=torch.float64, device=dev)
+        if use_dist:
+            import torch.distributed as dist
+            dist.all_reduce(est, op=dist.ReduceOp.MAX)       # every rank must choose the same R
+        R = int(min(max(50, -(-args.region_ms // est.item())), 20000))
+        sampler = ClockSampler(local)
+        sampler.start()       # before the barrier: starting it takes a variable time on every rank
+        torch.cuda.synchronize()
+        barrier()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(R + 1)]
+        ev[0].record()
+        for r in range(R):
+            one_pass()
+            ev[r + 1].record()
+        stream.synchronize()
     torch.cuda.synchronize()
     barrier()
-    ms = s.elapsed_time(e)
-    launches = per_step_launches * args.steps
+    clocks = sampler.stop()
+    passes = torch.tensor([ev[r].elapsed_time(ev[r + 1]) for r in range(R)], dtype=torch.float64, device=dev)
     if use_dist:
         import torch.distributed as dist
-        t = torch.tensor([ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        dist.all_reduce(passes, op=dist.ReduceOp.MAX)
+    passes = passes.cpu()
+    ms = float(passes.median())                    # one pass of K steps
+    launches = per_step_launches * K * R
+    t_step = ms / K                                # ms per step = per launch of the fused kernel
 
-    # kernel-only duration for the roofline: the fused launches alone, same rotation, replayed
-    # from a CUDA graph (CUDA events around the replays, on the launching stream)
-    for (a, b) in sets:
-        b.moments = None
-    t_kernel = graph_region(torch, lambda i: ops.run_pair(*sets[i % NSETS]), NSETS, max(args.steps, 120), 3)
-    # The timed region lasts a few milliseconds, shorter than one nvidia-smi sampling period, so the
-    # sampler stays on while the same kernel keeps running (this measurement, then up to a second
-    # more of the same launches) until it has seen the GPU under load a few times.
-    t_end = time.perf_counter() + 1.0
-    while time.perf_counter() < t_end:
-        for i in range(NSETS * 40):
-            ops.run_pair(*sets[i % NSETS])
-        torch.cuda.synchronize()
-    clocks = sampler.stop()
+    parity_ok, timed_out, parity = check_headline(torch, sets, w, ex, dev, world)
 
     # context for the roofline fraction: a device-to-device copy (tensor.copy_, i.e. cudaMemcpyAsync)
     # that moves the same number of bytes (half read, half written), timed the same way
@@ -585,7 +660,6 @@ def run_ours(args):
     del psrc, pdst
 
     # ---- end to end through the C ABI with host buffers (pinned), copies inside the timed region
-    w = workloads.config1()
     h_up, h_bn = w["up"].pin_memory(), w["bn"].pin_memory()
     # Two buffer sets and three streams (upload, kernel, download): the upload of step i+1 and
     # the download of step i-1 overlap the kernel of step i, so both PCIe directions are busy at
@@ -595,98 +669,190 @@ def run_ours(args):
     h_outs = [torch.empty(sets[0][0].out.shape, dtype=torch.float32).pin_memory() for _ in range(DEPTH)]
     h_stats = [torch.empty((2, 256), dtype=torch.float32).pin_memory() for _ in range(DEPTH)]
     s_in, s_k, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    uploaded = [None] * DEPTH
-    computed = [None] * DEPTH
-    downloaded = [None] * DEPTH
     e2e_steps = max(4, min(args.steps, 12))
 
-    def e2e_step(i):
-        k = i % DEPTH
-        a0, b0 = sets[k]
-        with torch.cuda.stream(s_in):
-            if computed[k] is not None:
-                s_in.wait_event(computed[k])           # the previous kernel on this set has read its inputs
-            a0.x.copy_(h_up, non_blocking=True)
-            b0.x.copy_(h_bn, non_blocking=True)
-            uploaded[k] = torch.cuda.Event()
-            uploaded[k].record()
-        with torch.cuda.stream(s_k):
-            s_k.wait_event(uploaded[k])
-            if downloaded[k] is not None:
-                s_k.wait_event(downloaded[k])          # the previous outputs of this set have left the device
-            ops.run_pair(a0, b0)
-            computed[k] = torch.cuda.Event()
-            computed[k].record()
-        with torch.cuda.stream(s_out):
-            s_out.wait_event(computed[k])
-            if downloaded[k] is not None:
-                downloaded[k].synchronize()            # the host has finished with this pinned buffer
-            h_outs[k].copy_(a0.out, non_blocking=True)
-            h_stats[k][0].copy_(b0.mean, non_blocking=True)
-            h_stats[k][1].copy_(b0.invstd, non_blocking=True)
-            downloaded[k] = torch.cuda.Event()
-            downloaded[k].record()
+    def e2e_run(with_kernel):
+        """ms per step of the pipelined upload / kernel / download loop; without the kernel it is
+        the same copies on the same streams and buffers: what the host link alone allows."""
+        uploaded, computed, downloaded = [None] * DEPTH, [None] * DEPTH, [None] * DEPTH
 
-    def e2e_drain():
-        for ev in downloaded:
-            if ev is not None:
-                ev.synchronize()                       # the caller holds every result
-    for i in range(DEPTH):
-        e2e_step(i)
-    e2e_drain()
-    torch.cuda.synchronize()
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(e2e_steps):
-        e2e_step(i)
-    e2e_drain()
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps      # host clock: it ends when the results are on the host
-    a0, b0 = sets[0]
-    h_out = h_outs[0]
-    if use_dist:
-        import torch.distributed as dist
-        t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+        def e2e_step(i):
+            k = i % DEPTH
+            a0, b0 = sets[k]
+            with torch.cuda.stream(s_in):
+                if computed[k] is not None:
+                    s_in.wait_event(computed[k])           # the previous kernel on this set has read its inputs
+                a0.x.copy_(h_up, non_blocking=True)
+                b0.x.copy_(h_bn, non_blocking=True)
+                uploaded[k] = torch.cuda.Event()
+                uploaded[k].record()
+            with torch.cuda.stream(s_k):
+                s_k.wait_event(uploaded[k])
+                if downloaded[k] is not None:
+                    s_k.wait_event(downloaded[k])          # the previous outputs of this set have left the device
+                if with_kernel:
+                    if ex is not None:
+                        ex.run_pair(a0, b0)
+                    else:
+                        ops.run_pair(a0, b0)
+                computed[k] = torch.cuda.Event()
+                computed[k].record()
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(computed[k])
+                if downloaded[k] is not None:
+                    downloaded[k].synchronize()            # the host has finished with this pinned buffer
+                h_outs[k].copy_(a0.out, non_blocking=True)
+                h_stats[k][0].copy_(b0.mean, non_blocking=True)
+                h_stats[k][1].copy_(b0.invstd, non_blocking=True)
+                downloaded[k] = torch.cuda.Event()
+                downloaded[k].record()
+
+        def e2e_drain():
+            for evd in downloaded:
+                if evd is not None:
+                    evd.synchronize()                      # the caller holds every result
+        for i in range(DEPTH):
+            e2e_step(i)
+        e2e_drain()
+        torch.cuda.synchronize()
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(e2e_steps):
+            e2e_step(i)
+        e2e_drain()
+        t_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps     # host clock: it ends when the results are on the host
+        if use_dist:
+            import torch.distributed as dist
+            t = torch.tensor([t_ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            t_ms = float(t.item())
+        return t_ms
+
+    e2e_ms = e2e_run(True)
+    copy_ms = e2e_run(False)
     h2d = h_up.numel() * 4 + h_bn.numel() * 4
-    d2h = h_out.numel() * 4 + h_stats[0].numel() * 4
+    d2h = h_outs[0].numel() * 4 + h_stats[0].numel() * 4
 
     line = {
         "metric": METRIC,
-        "value": round(world * nbytes * args.steps / ms / 1e6, 1), "unit": "GB/s", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 5),
+        "value": round(world * nbytes * K / ms / 1e6, 1), "unit": "GB/s", "n_gpus": world,
+        "steps": K, "warmup": args.warmup, "ms_per_step": round(t_step, 5),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "l2": f"steps rotate over {NSETS} independent buffer sets "
                                f"({NSETS * nbytes >> 20} MiB in total, L2 is 126 MB)",
-                   "launch": ("CUDA graph of %d steps, replayed" % GRAPH_STEPS) if graph is not None else "direct launches",
-                   "parallelism": f"batch-sharded x{world}", "collective": collective},
+                   "launch": launch_mode,
+                   "timed": {"passes": R, "steps_per_pass": K, "region_ms": round(float(passes.sum()), 2),
+                             "us_per_step_median": round(t_step * 1e3, 3),
+                             "us_per_step_min": round(float(passes.min()) / K * 1e3, 3),
+                             "us_per_step_max": round(float(passes.max()) / K * 1e3, 3),
+                             "us_per_step_mean": round(float(passes.mean()) / K * 1e3, 3),
+                             "rule": "every pass = K steps between two CUDA events on the launching stream, "
+                                     "max over ranks per pass, median over passes"},
+                   "parallelism": f"batch-sharded x{world} (every rank its own draw of the per-GPU batch)",
+                   "collective": collective, "host_binding": binding},
         "gpu_launches": launches,
+        "parity_ok": parity_ok, "exchange_timed_out": timed_out, "parity": parity,
         "e2e": {"value": round(world * nbytes / e2e_ms / 1e6, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 4),
+                "copy_only_ms_per_step": round(copy_ms, 4), "frac_of_copy_only": round(copy_ms / e2e_ms, 3),
                 "pipeline": "2 buffer sets, upload / kernel / download streams overlapped"},
-        "roofline": {"bound": "hbm", "achieved": round(nbytes / t_kernel / 1e6, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(nbytes / t_kernel / 1e6 / peak, 4), "traffic": NCU_TRAFFIC_BYTES,
-                     "peak_kind": peak_kind, "kernel": "fused_kernel<UpsampleRole,BnStatsRole>",
-                     "kernel_us": round(t_kernel * 1e3, 2),
+        "roofline": {"bound": "hbm", "achieved": round(nbytes / t_step / 1e6, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(nbytes / t_step / 1e6 / peak, 4), "traffic": NCU_TRAFFIC_BYTES.get(kernel_name),
+                     "peak_kind": peak_kind, "kernel": kernel_name,
+                     "kernel_us": round(t_step * 1e3, 2),
+                     "kernel_us_source": "the timed region: its only launches are this kernel",
                      "same_bytes_memcpy_d2d_us": round(t_copy * 1e3, 2),
                      "same_read_write_mix_bare_kernel_us": round(t_mix * 1e3, 2),
                      "write_only_bare_kernel_gbs": round(wr / t_wr / 1e6, 1)},
         "clocks": clocks,
     }
-    if rank == 0 and world == 1:
-        cpu_ms, cores = cpu_pair_cfg1(torch, 5, 1)
-        line["cpu_baseline"] = {"value": round(CFG1_BYTES / cpu_ms / 1e6, 3), "unit": "GB/s", "cores": cores,
-                                "kind": "port", "sample": "5 full passes of configuration 1 with PyTorch CPU operators"}
-        if not args.no_extras:
-            line["pairs"] = extras(torch, ops, crypto, workloads, dev, max(20, min(args.steps, 200)), 3, peak, barrier)
     if use_dist and not args.no_extras:
+        line["dl_sharded"] = dl_sharded(torch, ops, sharding, workloads, dev, rank, world, barrier, peak)
         sharded = crypto_sharded(torch, crypto, sharding, workloads, dev, rank, world, barrier)
         if rank == 0:
             line["crypto_sharded"] = sharded
     if rank == 0:
+        if not args.no_extras and world == 1:
+            line["pairs"] = extras(torch, ops, crypto, workloads, dev, max(20, min(args.steps, 200)), 3, peak, barrier)
+        torch.cuda.synchronize()
+        cpu_ms, cores = cpu_pair_cfg1(torch, 5, 1)
+        line["cpu_baseline"] = {"value": round(CFG1_BYTES / cpu_ms / 1e6, 3), "unit": "GB/s", "cores": cores,
+                                "kind": "port", "sample": "5 full passes of configuration 1 with PyTorch CPU operators"}
         print(json.dumps(line), flush=True)
     if use_dist:
-        shutdown(torch, graph)
+        wait_for_rank0(rank)
+        shutdown(torch, graphs)
+
+
+def wait_for_rank0(rank):
+    """Ranks other than 0 sleep on the rendezvous store until rank 0 has timed the CPU baseline
+    and printed the line: a collective barrier here would have them spin on the host cores
+    that the CPU baseline is being measured on."""
+    import torch.distributed as dist
+    store = dist.distributed_c10d._get_default_store()
+    if rank == 0:
+        store.set("hfuse_bench_line_printed", "1")
+    else:
+        store.wait(["hfuse_bench_line_printed"])
+
+
+def dl_sharded(torch, ops, sharding, workloads, dev, rank, world, barrier, peak):
+    """Configuration 2 split over the ranks (strong scaling: the total work is fixed): the im2col
+    batch of 32 and the 2^24 histogram values are cut into one contiguous shard per GPU, every rank
+    runs the fused im2col + histc pair on its shard, and the 256 counts are summed over ranks with
+    an NCCL all-reduce on the same stream.  Time = max over ranks of the device time per step
+    (fused launch + all-reduce, replayed from a CUDA graph); the results are compared with the
+    oracle on the unsplit inputs outside the timed region."""
+    import numpy as np
+    import torch.distributed as dist
+    from oracle import dl
+    w = workloads.config2()
+    NS = 4
+    im = sharding.shard_batch(w["im"], rank, world).contiguous()
+    hv = sharding.shard_flat(w["hist"], rank, world).contiguous()
+    sets = [(ops.Im2col(im.to(dev), **w["im2col"]), ops.Histc(hv.to(dev), w["bins"], w["lo"], w["hi"])) for _ in range(NS)]
+    stream = torch.cuda.Stream(dev)
+
+    def step(i):
+        a, b = sets[i % NS]
+        ops.run_pair(a, b)
+        sharding.allreduce_counts(b.counts)
+    with torch.cuda.stream(stream):
+        for i in range(2 * NS):
+            step(i)
+        stream.synchronize()
+        G = 6 * NS
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+            for i in range(G):
+                step(i)
+        graph.replay()
+        stream.synchronize()
+        barrier()
+        reps = 20
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
+        ev[0].record()
+        for r in range(reps):
+            graph.replay()
+            ev[r + 1].record()
+        stream.synchronize()
+    t = torch.tensor([ev[r].elapsed_time(ev[r + 1]) for r in range(reps)], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    us = float(t.median()) / G * 1e3
+    # parity, outside the timed region
+    want_counts = dl.histc_torch(w["hist"], w["bins"], w["lo"], w["hi"])
+    ok = True
+    for a, b in sets:
+        ok &= bool(np.array_equal(b.counts.cpu().numpy().view(np.uint32), want_counts))
+    ok &= bool(torch.equal(sets[0][0].out.cpu(), dl.im2col_torch(im, 3, 3, 1, 1, 1, 1, 1, 1)))
+    flag = torch.tensor([int(ok)], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    del graph
+    return {"workload": f"config 2 split over {world} GPUs: im2col batch {im.shape[0]} and {hv.numel()} histogram values per GPU",
+            "scaling": "strong", "us_per_step": round(us, 2), "GB_per_s_total": round(CFG2_BYTES / us / 1e3, 1),
+            "frac_of_hbm_peak_per_gpu": round(CFG2_BYTES / world / us / 1e3 / peak, 3),
+            "collective": "NCCL all-reduce of the 256 uint32 counts on the launching stream",
+            "parity_ok": bool(flag.item())}
 
 
 def run_tune_share(args, torch, _lib, ex, sets, nsets, dev, rank, barrier, use_dist):
@@ -802,13 +968,6 @@ def shutdown(torch, graph):
     os._exit(0)
 
 
-# DRAM bytes (read + write) per launch of the headline fused kernel from the committed ncu
-# capture (profiles/fused_upsample_bnstats_cfg1.md): 51.69 MB read + 49.34 MB written.  It is
-# below the algorithmic 154,142,720 B because part of the output is still dirty in L2 when an
-# isolated launch ends.
-NCU_TRAFFIC_BYTES = 101_030_656
-
-
 def run_only(args, torch, ops, crypto, workloads, dev):
     """One kernel or pair on its benchmark configuration, for profiling:
     --only cfg0|cfg1|cfg2|cfg3|cfg4|histc_maxpool|histc_upsample|histc_bnstats --mode fused|b2b|a|b [--graph]; cfg1 also takes --mode xchg, the
@@ -907,6 +1066,9 @@ def run_tune(args, torch, ops, crypto, workloads, dev):
                                 "all": times}
         del sets
         torch.cuda.empty_cache()
+    if args.tune_skip_crypto:
+        print(json.dumps(result))
+        return
     # crypto: reduced sweeps (2^27 nonces for the ALU hashes, 2^23 for ethash and for whatever
     # is paired with ethash: the benchmark configurations give both halves the same count)
     c3, c4 = workloads.config3(), workloads.config4(dev)
@@ -1023,6 +1185,8 @@ def main():
     ap.add_argument("--count", type=int, default=1 << 24, help="nonces per step with --only cfg3|cfg4")
     ap.add_argument("--dag-items", type=int, default=8_388_608)
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--im2col-path", default="registers", choices=["registers", "bulk"],
+                    help="store path of the im2col role: register tiles + streaming stores, or shared-memory tile + bulk (TMA) stores")
     ap.add_argument("--pair-variant", type=int, default=-1,
                     help="force thread-range variant V of the headline pair (tuning aid; default: the compiled-in choice)")
     ap.add_argument("--tune-share", action="store_true",
@@ -1033,7 +1197,10 @@ def main():
     ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
                     help="N > 1: sum the batch-norm moments inside the fused kernel (peer memory) or with NCCL")
     ap.add_argument("--no-graph", action="store_true", help="time direct launches instead of CUDA-graph replays")
+    ap.add_argument("--region-ms", type=float, default=1000.0,
+                    help="length of the timed region: the K-step pass is repeated until it lasts about this long (at least 50 passes)")
     ap.add_argument("--tune", action="store_true", help="sweep all variants and print the best per kernel / pair")
+    ap.add_argument("--tune-skip-crypto", action="store_true", help="with --tune: sweep the DL kernels and pairs only")
     ap.add_argument("--study", action="store_true", help="speedup vs ratio of the standalone times, as JSON")
     ap.add_argument("--graph", action="store_true", help="with --only: replay the launches from a CUDA graph")
     args = ap.parse_args()

@@ -61,14 +61,17 @@ def exported_symbols() -> list[str]:
     names = list(DL_SOLO.values()) + [f"hfuse_{p}_f32" for p in DL_PAIRS]
     names += list(CRYPTO_SOLO.values()) + [f"hfuse_{p}_search" for p in CRYPTO_PAIRS]
     names += ["hfuse_exchange_create", "hfuse_exchange_local_handle", "hfuse_exchange_connect",
-              "hfuse_exchange_status", "hfuse_exchange_destroy", "hfuse_exchange_local_pointer",
+              "hfuse_exchange_status", "hfuse_exchange_clear_status", "hfuse_exchange_destroy", "hfuse_exchange_local_pointer",
               "hfuse_exchange_connect_pointers", "hfuse_exchange_set_timeout", "hfuse_bnstats_allreduce_f32",
               "hfuse_upsample_bnstats_allreduce_f32"]
     names += ["hfuse_ethash_make_cache", "hfuse_ethash_generate_dag"]
+    names += ["hfuse_comm_unique_id", "hfuse_comm_create", "hfuse_comm_destroy", "hfuse_bnstats_allreduce_nccl_f64",
+              "hfuse_histc_allreduce_counts", "hfuse_dag_broadcast", "hfuse_blake256_sha256d_search_sharded",
+              "hfuse_sia_ethash_search_sharded"]
     names += ["hfuse_maxpool2d_backward_f32", "hfuse_bn_backward_f32", "hfuse_maxpool_backward_bn_backward_f32"]
     names += ["hfuse_error_string", "hfuse_version", "hfuse_bnstats_workspace_bytes", "hfuse_bnstats_noalloc_f32",
               "hfuse_bnstats_finalize_f64", "hfuse_hits_reset", "hfuse_hash_batch", "hfuse_tune_set",
-              "hfuse_tune_describe", "hfuse_tune_set_share", "hfuse_xoshiro256ss_fill", "hfuse_int32_probe", "hfuse_hbm_probe", "hfuse_shard_range"]
+              "hfuse_tune_describe", "hfuse_tune_set_share", "hfuse_tune_option", "hfuse_xoshiro256ss_fill", "hfuse_int32_probe", "hfuse_hbm_probe", "hfuse_shard_range"]
     return names
 
 
@@ -113,6 +116,7 @@ def lib() -> C.CDLL:
     L.hfuse_exchange_local_handle.restype, L.hfuse_exchange_local_handle.argtypes = _i, [_p, C.c_char_p]
     L.hfuse_exchange_connect.restype, L.hfuse_exchange_connect.argtypes = _i, [_p, C.c_char_p]
     L.hfuse_exchange_status.restype, L.hfuse_exchange_status.argtypes = _i, [_p, C.POINTER(_i)]
+    L.hfuse_exchange_clear_status.restype, L.hfuse_exchange_clear_status.argtypes = _i, [_p, _p]
     L.hfuse_exchange_local_pointer.restype, L.hfuse_exchange_local_pointer.argtypes = _i, [_p, C.POINTER(C.c_void_p)]
     L.hfuse_exchange_connect_pointers.restype = _i
     L.hfuse_exchange_connect_pointers.argtypes = [_p, C.POINTER(C.c_void_p)]
@@ -127,6 +131,17 @@ def lib() -> C.CDLL:
     L.hfuse_bn_backward_f32.restype, L.hfuse_bn_backward_f32.argtypes = _i, BNB + [_p]
     L.hfuse_maxpool_backward_bn_backward_f32.restype = _i
     L.hfuse_maxpool_backward_bn_backward_f32.argtypes = MPB + BNB + [_p]
+    L.hfuse_comm_unique_id.restype, L.hfuse_comm_unique_id.argtypes = _i, [C.c_char_p]
+    L.hfuse_comm_create.restype, L.hfuse_comm_create.argtypes = _i, [_i, _i, C.c_char_p, C.POINTER(_p)]
+    L.hfuse_comm_destroy.restype, L.hfuse_comm_destroy.argtypes = _i, [_p]
+    L.hfuse_bnstats_allreduce_nccl_f64.restype = _i
+    L.hfuse_bnstats_allreduce_nccl_f64.argtypes = [_p, _p, _i, _f, _p, _p, _p]
+    L.hfuse_histc_allreduce_counts.restype, L.hfuse_histc_allreduce_counts.argtypes = _i, [_p, _p, _i, _p]
+    L.hfuse_dag_broadcast.restype, L.hfuse_dag_broadcast.argtypes = _i, [_p, _p, _sz, _i, _p]
+    L.hfuse_blake256_sha256d_search_sharded.restype = _i
+    L.hfuse_blake256_sha256d_search_sharded.argtypes = SEARCH + SEARCH + [_i, _i, _p]
+    L.hfuse_sia_ethash_search_sharded.restype = _i
+    L.hfuse_sia_ethash_search_sharded.argtypes = SEARCH + ETHASH + [_i, _i, _p]
     L.hfuse_ethash_make_cache.restype, L.hfuse_ethash_make_cache.argtypes = _i, [C.c_char_p, _u32, _p]
     L.hfuse_ethash_generate_dag.restype = _i
     L.hfuse_ethash_generate_dag.argtypes = [_p, _u32, _p, _u32, _u32, _p]
@@ -136,6 +151,7 @@ def lib() -> C.CDLL:
     L.hfuse_tune_set.restype, L.hfuse_tune_set.argtypes = _i, [C.c_char_p, _i, _i]
     L.hfuse_tune_describe.restype, L.hfuse_tune_describe.argtypes = _i, [C.c_char_p, _i, C.c_char_p, _sz]
     L.hfuse_tune_set_share.restype, L.hfuse_tune_set_share.argtypes = _i, [C.c_char_p, _i]
+    L.hfuse_tune_option.restype, L.hfuse_tune_option.argtypes = _i, [C.c_char_p, _i]
     L.hfuse_xoshiro256ss_fill.restype, L.hfuse_xoshiro256ss_fill.argtypes = None, [_u64, _p, _sz]
     L.hfuse_shard_range.restype = _i
     L.hfuse_shard_range.argtypes = [_u64, _i, _i, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
@@ -160,6 +176,10 @@ def tune_set(name: str, variant: int = -1, blocks_per_sm: int = 0) -> None:
 
 def tune_set_share(name: str, permille: int = -1) -> None:
     check(lib().hfuse_tune_set_share(name.encode(), permille), f"tune_set_share({name})")
+
+
+def tune_option(name: str, value: int) -> None:
+    check(lib().hfuse_tune_option(name.encode(), value), f"tune_option({name})")
 
 
 def tune_variants(name: str) -> list[str]:

@@ -57,6 +57,25 @@ __device__ __forceinline__ void stg_stream_2xi64(long long* p, long long a, long
     asm volatile("st.global.cs.v2.s64 [%0], {%1,%2};" ::"l"(p), "l"(a), "l"(b) : "memory");
 }
 
+// ---- bulk (TMA) copies from shared to global memory ----------------------------------------
+// Untiled form: both addresses 16-byte aligned, size a multiple of 16 bytes.  The shared-memory
+// source is read by the async proxy, so the threads that filled it with ordinary stores run
+// fence_proxy_async_shared() before the barrier that precedes the copy.  Groups are per thread:
+// the thread that issued and committed the copies is the one that waits for them.
+__device__ __forceinline__ void fence_proxy_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void bulk_store(void* gdst, const void* ssrc, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(__cvta_generic_to_global(gdst)),
+                 "r"((uint32_t)__cvta_generic_to_shared(ssrc)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all but the newest N groups of this thread have finished READING their shared-memory source
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+// all but the newest N groups of this thread are complete (written)
+template <int N>
+__device__ __forceinline__ void bulk_wait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+
 // ---- division by a launch-time constant --------------------------------------------------
 // q = n / d for n < 2^31 as one multiply-high, one add and one shift
 // (m = floor(2^32 * (2^s - d) / d) + 1, s = ceil(log2 d); the sum cannot overflow for n < 2^31).

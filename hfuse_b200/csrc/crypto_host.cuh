@@ -76,7 +76,7 @@ int prep_common(uint64_t start, uint64_t count, const uint8_t* target32, hfuse_h
                 SearchCommon& c) {
     if (!target32 || !hits) return HFUSE_ERR_BAD_ARG;
     if (nonce32 && count > (1ull << 32)) return HFUSE_ERR_TOO_LARGE;   // the nonce space itself
-    if (count > (1ull << 62)) return HFUSE_ERR_TOO_LARGE;
+    if (count > (1ull << 61)) return HFUSE_ERR_TOO_LARGE;                // a work-queue chunk must fit 32 bits
     c.start = start; c.count = count; c.hits = hits; c.out32 = nullptr; c.mix32 = nullptr; c.one = 1u;
     for (int i = 0; i < 8; ++i) c.target[i] = be32(target32 + 4 * i);
     return HFUSE_OK;
@@ -144,6 +144,9 @@ constexpr int kCryptoSoloVariants = 9;
 template <class RA, class RB>
 int dispatch_pair(const char* name, int default_variant, typename RA::Args a, typename RB::Args b, cudaStream_t s) {
     const Tune t = tune_get(name);
+    // each half draws its nonces from the cursor in its own record: one record for both halves
+    // would make them share a cursor and skip nonces
+    if (a.c.hits == b.c.hits) return HFUSE_ERR_BAD_ARG;
     // the work-queue cursors must start at zero whatever the caller left in the records
     if (cudaMemsetAsync(&a.c.hits->reserved, 0, sizeof(uint32_t), s) != cudaSuccess ||
         cudaMemsetAsync(&b.c.hits->reserved, 0, sizeof(uint32_t), s) != cudaSuccess)

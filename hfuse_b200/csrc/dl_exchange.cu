@@ -13,24 +13,21 @@ struct hfuse_exchange {
     unsigned char* local = nullptr;
     unsigned char* peer[hfuse::kXchgMaxRanks] = {};
     bool opened[hfuse::kXchgMaxRanks] = {};
-    unsigned uses[hfuse::kXchgSlots] = {};
-    unsigned long long calls = 0;
     unsigned long long timeout_ns = 5ull * 1000 * 1000 * 1000;   // 5 s per exchange wait unless changed
     bool connected = false;
 };
 
 namespace {
 
-int next_use(hfuse_exchange* ex, int C, BnXchg& x) {
+// What a launch needs to know about the exchange.  Nothing here changes from call to call: the
+// slot and epoch of a call are derived on the device from the counter in the buffer's header,
+// which the kernel itself advances, so a launch that fails after this point (or is captured in a
+// graph and replayed) cannot put this rank out of step with the others.
+int describe_exchange(hfuse_exchange* ex, int C, BnXchg& x) {
     if (!ex || !ex->connected) return HFUSE_ERR_BAD_ARG;
     if (C != ex->C) return HFUSE_ERR_BAD_ARG;
-    const unsigned slot = (unsigned)(ex->calls % hfuse::kXchgSlots);
-    ex->uses[slot] += 1;
-    ex->calls += 1;
     x.world = ex->world;
     x.rank = ex->rank;
-    x.slot = slot;
-    x.epoch = ex->uses[slot];
     x.timeout_ns = ex->timeout_ns;
     for (int r = 0; r < hfuse::kXchgMaxRanks; ++r) x.peer[r] = ex->peer[r];
     return HFUSE_OK;
@@ -121,6 +118,15 @@ int hfuse_exchange_status(hfuse_exchange* ex, int* timed_out) {
     return HFUSE_OK;
 }
 
+int hfuse_exchange_clear_status(hfuse_exchange* ex, hfuse_stream_t stream) {
+    if (!ex) return HFUSE_ERR_BAD_ARG;
+    if (cudaMemsetAsync(ex->local + offsetof(XchgLayout, status), 0, sizeof(unsigned), S_(stream)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return HFUSE_ERR_LAUNCH;
+    }
+    return HFUSE_OK;
+}
+
 int hfuse_exchange_destroy(hfuse_exchange* ex) {
     if (!ex) return HFUSE_OK;
     for (int r = 0; r < ex->world; ++r)
@@ -134,7 +140,7 @@ int hfuse_exchange_destroy(hfuse_exchange* ex) {
 int hfuse_bnstats_allreduce_f32(HFUSE_BNSTATS_PARAMS(), hfuse_exchange* ex, hfuse_stream_t stream) {
     BnStatsArgs a;
     if (int rc = prep_bnstats(BNSTATS_NAMES(), a)) return rc;
-    if (int rc = next_use(ex, C, a.xchg)) return rc;
+    if (int rc = describe_exchange(ex, C, a.xchg)) return rc;
     return dispatch_solo<BnStatsXchgRole>("bnstats", kDefaultSolo_bnstats, a, S_(stream));
 }
 
@@ -144,7 +150,7 @@ int hfuse_upsample_bnstats_allreduce_f32(HFUSE_UPSAMPLE_PARAMS(a_), HFUSE_BNSTAT
     BnStatsArgs b;
     if (int rc = prep_upsample(UPSAMPLE_NAMES(a_), a)) return rc;
     if (int rc = prep_bnstats(BNSTATS_NAMES(b_), b)) return rc;
-    if (int rc = next_use(ex, b_C, b.xchg)) return rc;
+    if (int rc = describe_exchange(ex, b_C, b.xchg)) return rc;
     // Its own tuning entry.  The statistics range sends its moments, then works through a share of
     // the upsample and only then waits for the peers, so the best split gives that range more
     // threads than the single-GPU pair does (it should finish its own work early).

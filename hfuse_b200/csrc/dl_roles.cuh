@@ -29,7 +29,10 @@ struct Im2colArgs {
     int kh, kw, ph, pw, sh, sw, dh, dw;
     int Hc, Wc;
     int mode;   // 0 = generic (one output element per item), 1 = 3x3 stride-1 tile path (4 columns per item),
-                // 2 = the same with 8 columns per item and 256-bit stores (pad 1, Wc % 8 == 0, col 32-byte aligned)
+                // 2 = the same with 8 columns per item and 256-bit stores (pad 1, Wc % 8 == 0, col 32-byte aligned),
+                // 3 = 3x3 stride-1 pad-1 through a shared-memory tile and bulk (TMA) stores (run_bulk)
+    int band, bands;          // mode 3: output rows per work unit, units per plane
+    FastDiv div_bands;        // mode 3: by bands
     FastDiv div_w4, div_hc;   // tile paths: by Wc/4 (mode 1) or Wc/8 (mode 2), and by Hc
     FastDiv div_wc, div_taps, div_kw;   // generic path with fewer than 2^31 outputs (small != 0)
     int small;
@@ -37,8 +40,68 @@ struct Im2colArgs {
 
 struct Im2colRole {
     using Args = Im2colArgs;
-    static int smem_bytes(const Args&, int) { return 0; }
+    // mode 3: two buffers of three column-shifted copies of band + 2 input rows
+    static int smem_bytes(const Args& a, int) { return a.mode == 3 ? 2 * 3 * (a.band + 2) * a.Wc * (int)sizeof(float) : 0; }
     static int plan(Args&, int /*T*/, int /*grid*/) { return 0; }
+
+    // 3x3 / stride 1 / pad 1 / dilation 1 (so Wc == W, Hc == H), W % 4 == 0, through shared memory.
+    // Work unit = (plane, band of `band` output rows).  The role loads the band's band + 2 input
+    // rows once (16-byte loads) and lays them down three times in shared memory, shifted by one
+    // column to the right, not at all, and one to the left, with the zero padding written in:
+    // copy j, row r, column w holds im[h0 - 1 + r][w - 1 + j].  Tap (i, j) of the band is then the
+    // CONTIGUOUS block of rows i .. i + band - 1 of copy j, and its place in `col` is contiguous
+    // too (rows h0 .. h0 + band - 1 of one tap plane), so each of the nine taps leaves as one bulk
+    // copy of band * Wc * 4 bytes issued by one thread.  Two buffers: the copies of one unit drain
+    // while the next unit is loaded.
+    template <int T, int BAR>
+    static __device__ __forceinline__ void run_bulk(const Args& a, const RoleCtx& ctx) {
+        const int Wc = a.Wc, W4 = a.W >> 2;
+        const unsigned copy_elems = (unsigned)(a.band + 2) * Wc;
+        float* sm = reinterpret_cast<float*>(ctx.smem);
+        const unsigned units = (unsigned)a.N * a.C * a.bands;
+        const size_t tap_stride = (size_t)a.Hc * a.Wc;
+        int buf = 0;
+        for (unsigned u = ctx.block; u < units; u += ctx.nblocks, buf ^= 1) {
+            unsigned bi;
+            const unsigned plane = fast_divmod(u, a.div_bands, bi);
+            const int h0 = (int)bi * a.band;
+            const int nrows = min(a.band, a.Hc - h0);
+            float* tile = sm + (size_t)buf * 3 * copy_elems;
+            // the copies that read this buffer two units ago must have finished reading it
+            if (ctx.tid == 0) bulk_wait_read<1>();
+            role_sync<BAR, T>();
+            const float* src = a.im + (size_t)plane * a.H * a.W;
+            for (int it = ctx.tid; it < (nrows + 2) * W4; it += T) {
+                const int r = it / W4, m = it - r * W4;
+                const int hi = h0 - 1 + r;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (hi >= 0 && hi < a.H) v = __ldg(reinterpret_cast<const float4*>(src + (size_t)hi * a.W + 4 * m));
+                float* row = tile + r * Wc + 4 * m;
+                *reinterpret_cast<float4*>(row + copy_elems) = v;                 // j = 1: in place
+                float* c0 = row + 1;                                              // j = 0: one column to the right
+                c0[0] = v.x; c0[1] = v.y; c0[2] = v.z;
+                if (m + 1 < W4) c0[3] = v.w;
+                if (m == 0) row[0] = 0.f;                                         // left padding
+                float* c2 = row + 2 * copy_elems - 1;                             // j = 2: one column to the left
+                if (m > 0) c2[0] = v.x;
+                c2[1] = v.y; c2[2] = v.z; c2[3] = v.w;
+                if (m + 1 == W4) c2[4] = 0.f;                                     // right padding
+            }
+            fence_proxy_async_shared();
+            role_sync<BAR, T>();
+            if (ctx.tid == 0) {
+                float* dst = a.col + (size_t)plane * 9 * tap_stride + (size_t)h0 * Wc;
+                const uint32_t bytes = (uint32_t)nrows * Wc * (uint32_t)sizeof(float);
+#pragma unroll
+                for (int i = 0; i < 3; ++i)
+#pragma unroll
+                    for (int j = 0; j < 3; ++j)
+                        bulk_store(dst + (size_t)(i * 3 + j) * tap_stride, tile + j * copy_elems + i * Wc, bytes);
+                bulk_commit();
+            }
+        }
+        if (ctx.tid == 0) bulk_wait<0>();      // shared memory must outlive the copies that read it
+    }
 
     // 3x3 / stride 1 / dilation 1, Wc % 4 == 0: one item = four adjacent
     // output columns of one (plane, row).  The thread reads the 3 x 6 input
@@ -193,7 +256,8 @@ struct Im2colRole {
 
     template <int T, int BAR>
     static __device__ __forceinline__ void run(const Args& a, const RoleCtx& ctx) {
-        if (a.mode == 2) run_k3s1_wide<T>(a, ctx);
+        if (a.mode == 3) run_bulk<T, BAR>(a, ctx);
+        else if (a.mode == 2) run_k3s1_wide<T>(a, ctx);
         else if (a.mode == 1) run_k3s1<T>(a, ctx);
         else run_generic<T>(a, ctx);
     }
@@ -520,12 +584,14 @@ struct HistcArgs {
     long long n;
     int nbins;
     float lo, hi;
+    float fbins;        // nbins as fp32 (exact: nbins <= 2^24)
     float range;        // hi - lo, rounded to fp32
     float inv_range;    // 1 / range, only meaningful when range_pow2
     int range_pow2;     // range is a power of two: multiplying by inv_range equals dividing by range
-    unsigned* counts;   // zeroed by the caller (the entry point clears it on the stream)
+    unsigned* counts;   // zeroed on the stream before the kernel's flush (see the entry points)
     int copies;         // private shared-memory histograms per role (0 = global atomics only)
     int lane_private;   // shared histogram laid out [bin][32 lanes]: lane l only ever touches bank l
+    int fast;           // fewer than 2^31 16-byte items: 32-bit indices and the peeled loop
 };
 
 struct HistcRole {
@@ -559,14 +625,72 @@ struct HistcRole {
     // bin of v, or -1 when v is outside [lo, hi] or NaN
     static __device__ __forceinline__ int bin_of(const Args& a, float v) {
         if (!(v >= a.lo && v <= a.hi)) return -1;
-        const float t = __fmul_rn(__fsub_rn(v, a.lo), (float)a.nbins);
+        const float t = __fmul_rn(__fsub_rn(v, a.lo), a.fbins);
         const float q = a.range_pow2 ? __fmul_rn(t, a.inv_range) : __fdiv_rn(t, a.range);
         const int b = (int)q;
         return b == a.nbins ? b - 1 : b;
     }
 
-    // SHARED selects the address space at compile time: the shared-memory histogram is
-    // updated with `red.shared` (no return value, no generic-address atomics)
+    // The same bin with as few instructions as the arithmetic allows (the sweep is bound by
+    // instruction issue, not by memory, when it spends thirty instructions on a value):
+    // d = v - lo is computed anyway and is >= 0 exactly when v >= lo (a difference of two
+    // floats is zero only if they are equal, and NaN compares false), so the range test costs
+    // one more compare (v <= hi); the products and the quotient are rounded one by one in the
+    // order above, so the bin is the same; q (at most nbins, and a shared-memory histogram has
+    // at most a few thousand bins) truncates by adding 2^23 towards zero and reading the
+    // mantissa; the top edge (v == hi gives q == nbins) is a min.  The reduction is predicated,
+    // so whatever an out-of-range value produced as a bin is never used.
+    template <int SHIFT, bool POW2>
+    static __device__ __forceinline__ void count(const Args& a, float v, uint32_t sbase, int last) {
+        const float d = __fsub_rn(v, a.lo);
+        const float t = __fmul_rn(d, a.fbins);
+        const float q = POW2 ? __fmul_rn(t, a.inv_range) : __fdiv_rn(t, a.range);
+        const int b = min(__float_as_int(__fadd_rz(q, 8388608.f)) & 0x7fffff, last);
+        if ((d >= 0.f) && (v <= a.hi)) red_shared_inc(sbase + ((uint32_t)b << SHIFT));
+    }
+
+    // Sweep over fewer than 2^31 16-byte items into a shared-memory histogram.  The items of a
+    // thread are i0 + k * stride; the first `full` groups of U items are in range for every
+    // thread, so the main loop carries no bounds checks, and the loads of group k + 1 are issued
+    // before group k is counted (every warp keeps loads in flight while its reductions drain).
+    template <int T, int SHIFT, bool POW2>
+    static __device__ __forceinline__ void sweep_fast(const Args& a, const RoleCtx& ctx, uint32_t sbase) {
+        constexpr int U = 4;
+        const int last = a.nbins - 1;
+        const uint32_t n4 = (uint32_t)(a.n >> 2);
+        const uint32_t stride = (uint32_t)ctx.nblocks * T;
+        const uint32_t full = n4 / (stride * U);
+        uint32_t i = (uint32_t)ctx.block * T + ctx.tid;
+        auto count4 = [&](const float4& v) {
+            count<SHIFT, POW2>(a, v.x, sbase, last); count<SHIFT, POW2>(a, v.y, sbase, last);
+            count<SHIFT, POW2>(a, v.z, sbase, last); count<SHIFT, POW2>(a, v.w, sbase, last);
+        };
+        if (full > 0) {
+            float4 nxt[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) nxt[u] = ldg_stream4(a.x + 4ull * (i + u * stride));
+            for (uint32_t k = 1; k < full; ++k) {
+                float4 v[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) v[u] = nxt[u];
+                i += U * stride;
+#pragma unroll
+                for (int u = 0; u < U; ++u) nxt[u] = ldg_stream4(a.x + 4ull * (i + u * stride));
+#pragma unroll
+                for (int u = 0; u < U; ++u) count4(v[u]);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) count4(nxt[u]);
+            i += U * stride;
+        }
+        for (; i < n4; i += stride) count4(ldg_stream4(a.x + 4ull * i));     // ragged end: fewer than U items per thread
+        if (ctx.block == 0)      // n % 4 values
+            for (long long j = 4ll * n4 + ctx.tid; j < a.n; j += T) count<SHIFT, POW2>(a, __ldg(a.x + j), sbase, last);
+    }
+
+    // General sweep: 64-bit indices, any histogram placement.  SHARED selects the address space at
+    // compile time: the shared-memory histogram is updated with `red.shared` (no return value, no
+    // generic-address atomics).  Used for 2^31 or more items and for the global-atomics layout.
     template <int T, bool SHARED>
     static __device__ __forceinline__ void sweep(const Args& a, const RoleCtx& ctx, unsigned* hist) {
         const long long n4 = a.n >> 2;
@@ -574,9 +698,6 @@ struct HistcRole {
         const int shift = (SHARED && a.lane_private) ? 5 : 0;
         const uint32_t sbase = SHARED ? (uint32_t)__cvta_generic_to_shared(hist) + (a.lane_private ? 4u * (ctx.tid & 31) : 0u)
                                       : 0u;
-        // Software pipeline: the 16-byte loads of the next iteration are issued before the
-        // current values are binned, so every warp keeps loads in flight while its shared
-        // reductions drain (the reductions cost about four cycles per warp instruction).
         constexpr int U = 4;
         const long long stride = (long long)ctx.nblocks * T;
         long long i = (long long)ctx.block * T + ctx.tid;
@@ -624,9 +745,22 @@ struct HistcRole {
         }
     }
 
+    template <int T, int SHIFT>
+    static __device__ __forceinline__ void sweep_fast_pick(const Args& a, const RoleCtx& ctx, uint32_t sbase) {
+        if (a.range_pow2) sweep_fast<T, SHIFT, true>(a, ctx, sbase);
+        else sweep_fast<T, SHIFT, false>(a, ctx, sbase);
+    }
+
+    // The counts are cleared by a small kernel launched just before this one, and this kernel is
+    // launched as its programmatic dependent: it starts while the clearing kernel runs and only
+    // waits for it here, before its first access to the counts.  Launched without that attribute
+    // the instruction returns at once (stream order has already done the waiting).
+    static __device__ __forceinline__ void wait_for_cleared_counts() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
     template <int T, int BAR>
     static __device__ __forceinline__ void run(const Args& a, const RoleCtx& ctx) {
         if (a.copies == 0) {
+            wait_for_cleared_counts();
             sweep<T, false>(a, ctx, a.counts);
             return;
         }
@@ -635,8 +769,15 @@ struct HistcRole {
         for (int i = ctx.tid; i < words; i += T) sh[i] = 0u;
         role_sync<BAR, T>();
         unsigned* hist = a.lane_private ? sh : sh + ((ctx.tid >> 5) % a.copies) * a.nbins;
-        sweep<T, true>(a, ctx, hist);
+        if (a.fast) {
+            const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(hist) + (a.lane_private ? 4u * (ctx.tid & 31) : 0u);
+            if (a.lane_private) sweep_fast_pick<T, 7>(a, ctx, sbase);
+            else sweep_fast_pick<T, 2>(a, ctx, sbase);
+        } else {
+            sweep<T, true>(a, ctx, hist);
+        }
         role_sync<BAR, T>();
+        wait_for_cleared_counts();
         for (int b = ctx.tid; b < a.nbins; b += T) {
             unsigned s = 0;
             if (a.lane_private) {
@@ -673,22 +814,45 @@ struct HistcRole {
 // folds them in rank order, so all ranks compute the same bits.  Slots rotate and epochs only
 // grow; a rank can run at most one call ahead of the slowest one (its next kernel cannot end
 // before every rank has delivered), so a slot is never overwritten before it has been read.
+// Slot and epoch of a call come from a call counter kept in the buffer's header ON THE DEVICE:
+// every block reads it when it starts, and the block that finishes last advances it.  The host
+// therefore passes nothing that changes from call to call, so a launch replayed from a CUDA graph
+// moves on to the next slot and epoch like a direct launch does, and a launch that failed on the
+// host leaves the counter where the other ranks' counters are.
 constexpr int kXchgMaxRanks = 8;
 constexpr int kXchgSlots = 4;
 constexpr int kXchgRowWords = 6;      // 5 used, padded to 48 bytes
 struct XchgLayout {                   // header of an exchange buffer
     unsigned status;                  // set to 1 when a wait ran out of time
-    unsigned pad[63];
+    unsigned calls;                   // exchange launches completed on this buffer
+    unsigned done;                    // blocks of the running launch that have finished their exchange work
+    unsigned pad[61];
     // followed by unsigned long long rows[kXchgSlots][kXchgMaxRanks][C][kXchgRowWords]
 };
 struct BnXchg {
     int world;                // 0: exchange disabled
     int rank;
-    unsigned slot;
-    unsigned epoch;           // use count of this slot, never 0 (the buffer starts zeroed)
     unsigned long long timeout_ns;
     unsigned char* peer[kXchgMaxRanks];   // exchange buffers of all ranks (peer[rank] is the local one)
 };
+struct XchgUse {              // which slot a launch writes, and the tag its words carry
+    unsigned slot;
+    unsigned epoch;           // use count of the slot, never 0 (the buffer starts zeroed)
+};
+__device__ __forceinline__ XchgUse xchg_use(const BnXchg& x) {
+    const volatile unsigned* calls = &reinterpret_cast<const XchgLayout*>(x.peer[x.rank])->calls;
+    const unsigned n = *calls;
+    return XchgUse{n % kXchgSlots, n / kXchgSlots + 1u};
+}
+// One thread per block, after the block's last exchange access: the last block to arrive moves
+// the buffer on to the next call and leaves the ticket at zero.
+__device__ __forceinline__ void xchg_block_done(const BnXchg& x, unsigned nblocks) {
+    XchgLayout* h = reinterpret_cast<XchgLayout*>(x.peer[x.rank]);
+    if (atomicAdd(&h->done, 1u) == nblocks - 1u) {
+        h->done = 0u;
+        atomicAdd(&h->calls, 1u);
+    }
+}
 __device__ __forceinline__ volatile unsigned long long* xchg_row(unsigned char* base, int C, unsigned slot, int src,
                                                                  int c) {
     unsigned long long* rows = reinterpret_cast<unsigned long long*>(base + sizeof(XchgLayout));
@@ -791,16 +955,16 @@ struct BnStatsRole {
 
     // Exchange form of finish(), in two halves, each run by all 32 lanes of one warp.
     // xchg_send: the channel's local moments are in lane 0; lane r stores them into rank r's buffer.
-    static __device__ __forceinline__ void xchg_send(const Args& a, int c, Moments m, int lane) {
+    static __device__ __forceinline__ void xchg_send(const Args& a, XchgUse use, int c, Moments m, int lane) {
         const BnXchg& x = a.xchg;
         const float mean_l = __shfl_sync(0xffffffffu, m.mean, 0);
         const float m2_l = __shfl_sync(0xffffffffu, m.m2, 0);
         const double n = (double)a.N * (double)a.HW, mu = (double)mean_l;
         const unsigned long long s1 = (unsigned long long)__double_as_longlong(n * mu);
         const unsigned long long s2 = (unsigned long long)__double_as_longlong((double)m2_l + n * mu * mu);
-        const unsigned long long tag = (unsigned long long)x.epoch << 32;
+        const unsigned long long tag = (unsigned long long)use.epoch << 32;
         if (lane < x.world) {          // lane r sends to rank r: the stores of all ranks go out side by side
-            volatile unsigned long long* row = xchg_row(x.peer[lane], a.C, x.slot, x.rank, c);
+            volatile unsigned long long* row = xchg_row(x.peer[lane], a.C, use.slot, x.rank, c);
             row[0] = tag | (s1 & 0xffffffffull);
             row[1] = tag | (s1 >> 32);
             row[2] = tag | (s2 & 0xffffffffull);
@@ -811,12 +975,12 @@ struct BnStatsRole {
 
     // xchg_collect: lane r waits (bounded) for rank r's row of channel c in the local buffer; the
     // rows are folded in rank order and lane 0 writes the channel's global statistics.
-    static __device__ __forceinline__ void xchg_collect(const Args& a, int c, int lane) {
+    static __device__ __forceinline__ void xchg_collect(const Args& a, XchgUse use, int c, int lane) {
         const BnXchg& x = a.xchg;
         double rs1 = 0.0, rs2 = 0.0, rn = 0.0;
         bool ok = true;
         if (lane < x.world) {
-            volatile unsigned long long* row = xchg_row(x.peer[x.rank], a.C, x.slot, lane, c);
+            volatile unsigned long long* row = xchg_row(x.peer[x.rank], a.C, use.slot, lane, c);
             unsigned long long t0, t1, w[5];
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
             for (;;) {
@@ -824,7 +988,7 @@ struct BnStatsRole {
                 for (int k = 0; k < 5; ++k) w[k] = row[k];
                 bool all = true;
 #pragma unroll
-                for (int k = 0; k < 5; ++k) all &= (unsigned)(w[k] >> 32) == x.epoch;
+                for (int k = 0; k < 5; ++k) all &= (unsigned)(w[k] >> 32) == use.epoch;
                 if (all) break;
                 __nanosleep(64);
                 asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
@@ -855,10 +1019,10 @@ struct BnStatsRole {
     // called by all 32 lanes of warp 0 with the channel's folded moments in lane 0.  DEFER: send
     // now, collect later (collect_deferred), so that the wait for the peers overlaps other work.
     template <bool XCHG, bool DEFER>
-    static __device__ __forceinline__ void complete(const Args& a, int c, Moments m, int lane) {
+    static __device__ __forceinline__ void complete(const Args& a, XchgUse use, int c, Moments m, int lane) {
         if (XCHG) {
-            xchg_send(a, c, m, lane);
-            if (!DEFER) xchg_collect(a, c, lane);
+            xchg_send(a, use, c, m, lane);
+            if (!DEFER) xchg_collect(a, use, c, lane);
         } else if (lane == 0) {
             finish(a, c, m);
         }
@@ -875,7 +1039,8 @@ struct BnStatsRole {
     template <int T>
     static __device__ __forceinline__ void collect_deferred(const Args& a, const RoleCtx& ctx) {
         if (a.S != 1 || (ctx.tid >> 5) != 0) return;
-        for (unsigned u = ctx.block; u < (unsigned)a.C; u += ctx.nblocks) xchg_collect(a, (int)u, ctx.tid & 31);
+        const XchgUse use = xchg_use(a.xchg);      // not advanced yet: this block has not reported done
+        for (unsigned u = ctx.block; u < (unsigned)a.C; u += ctx.nblocks) xchg_collect(a, use, (int)u, ctx.tid & 31);
     }
 
     template <int T, int BAR, bool XCHG, bool DEFER>
@@ -886,6 +1051,8 @@ struct BnStatsRole {
         float* sh = reinterpret_cast<float*>(ctx.smem);
         const int lane = ctx.tid & 31, warp = ctx.tid >> 5;
         const unsigned units = (unsigned)a.C * (unsigned)a.S;
+        XchgUse use{0u, 0u};
+        if (XCHG) use = xchg_use(a.xchg);
         int parity = 0;
         for (unsigned u = ctx.block; u < units; u += ctx.nblocks, parity ^= 1) {
             const unsigned c = u / a.S, s = u - c * a.S;
@@ -958,7 +1125,7 @@ struct BnStatsRole {
             Moments w = (lane < NW) ? Moments{buf[lane], buf[NW + lane], buf[2 * NW + lane]} : Moments{0.f, 0.f, 0.f};
             w = warp_merge(w);
             if (a.S == 1) {
-                complete<XCHG, DEFER>(a, (int)c, w, lane);
+                complete<XCHG, DEFER>(a, use, (int)c, w, lane);
                 continue;
             }
             // publish this slice; the block that takes the last ticket folds all slices
@@ -979,7 +1146,7 @@ struct BnStatsRole {
                 }
                 q = warp_merge(q);
                 if (lane == 0) a.tickets[c] = 0u;     // ready for the next call
-                complete<XCHG, false>(a, (int)c, q, lane);
+                complete<XCHG, false>(a, use, (int)c, q, lane);
             }
         }
     }
@@ -990,6 +1157,7 @@ struct BnStatsXchgRole : BnStatsRole {
     template <int T, int BAR>
     static __device__ __forceinline__ void run(const Args& a, const RoleCtx& ctx) {
         BnStatsRole::run_impl<T, BAR, true, false>(a, ctx);
+        if (ctx.tid == 0) xchg_block_done(a.xchg, (unsigned)ctx.nblocks);   // warp 0 did this block's exchange
     }
     // the two halves for a kernel that puts other work between sending and collecting
     template <int T, int BAR>
@@ -999,6 +1167,7 @@ struct BnStatsXchgRole : BnStatsRole {
     template <int T, int BAR>
     static __device__ __forceinline__ void run_late(const Args& a, const RoleCtx& ctx) {
         BnStatsRole::collect_deferred<T>(a, ctx);
+        if (ctx.tid == 0) xchg_block_done(a.xchg, (unsigned)ctx.nblocks);
     }
 };
 

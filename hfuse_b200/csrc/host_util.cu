@@ -20,6 +20,7 @@ const char* hfuse_error_string(int code) {
     case HFUSE_ERR_LAUNCH: return "CUDA reported an error at launch";
     case HFUSE_ERR_NO_DEVICE: return "no usable sm_100 device";
     case HFUSE_ERR_UNKNOWN_PAIR: return "unknown kernel or pair name";
+    case HFUSE_ERR_COMM: return "NCCL could not be loaded or one of its calls failed";
     case HFUSE_ERR_NOALLOC_LIMIT:
         return "more channels than the built-in scratch of the no-allocation entry point serves (HFUSE_NOALLOC_MAX_CHANNELS)";
     }
@@ -57,6 +58,15 @@ int hfuse_tune_set_share(const char* pair, int permille) {
     if (strcmp(pair, "upsample_bnstats_allreduce") != 0) return HFUSE_ERR_UNKNOWN_PAIR;
     std::lock_guard<std::mutex> lk(hfuse::tune_mutex());
     hfuse::tune_table()[pair].share_permille = permille;
+    return HFUSE_OK;
+}
+
+int hfuse_tune_option(const char* name, int value) {
+    if (!name) return HFUSE_ERR_BAD_ARG;
+    if (strcmp(name, "im2col_store_path") != 0) return HFUSE_ERR_UNKNOWN_PAIR;
+    if (value < 0 || value > 1) return HFUSE_ERR_BAD_ARG;
+    std::lock_guard<std::mutex> lk(hfuse::tune_mutex());
+    hfuse::option_table()[name] = value;
     return HFUSE_OK;
 }
 

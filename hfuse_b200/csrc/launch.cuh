@@ -77,11 +77,67 @@ inline Tune tune_get(const char* name) {
     return it == tune_table().end() ? Tune{} : it->second;
 }
 
+// ---- options: named integer switches between alternative code paths -----------------------
+// "im2col_store_path": 0 = register tiles and streaming stores (default), 1 = shared-memory tile
+// and bulk (TMA) stores where the shape allows it.
+inline std::map<std::string, int>& option_table() {
+    static std::map<std::string, int> t;
+    return t;
+}
+inline int option_get(const char* name) {
+    std::lock_guard<std::mutex> lk(tune_mutex());
+    auto it = option_table().find(name);
+    return it == option_table().end() ? 0 : it->second;
+}
+
+// more than 48 KB of dynamic shared memory has to be asked for once per kernel and device
+inline void allow_dynamic_smem(const void* func, size_t smem) {
+    if (smem <= 48 * 1024) return;
+    static std::mutex mu;
+    static std::map<std::pair<int, const void*>, size_t> granted;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(mu);
+    size_t& g = granted[{dev, func}];
+    if (g >= smem) return;
+    if (cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess) g = smem;
+    else (void)cudaGetLastError();
+}
+
 inline int check_launch() { return cudaGetLastError() == cudaSuccess ? HFUSE_OK : HFUSE_ERR_LAUNCH; }
+
+// One kernel launch.  `dependent` marks the kernel as the programmatic dependent of the launch
+// before it on the stream: it may start while that kernel is still running and meets it only at
+// its own `griddepcontrol.wait` (used by the roles whose output buffer is cleared by a small
+// kernel just ahead: the clearing then costs no gap on the stream).
+template <class... KArgs, class... Args>
+int launch_kernel(void (*kern)(KArgs...), int grid, int block, size_t smem, cudaStream_t s, bool dependent,
+                  Args&&... args) {
+    allow_dynamic_smem((const void*)kern, smem);
+    if (!dependent) {
+        kern<<<grid, block, smem, s>>>(args...);
+        return check_launch();
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return HFUSE_ERR_LAUNCH;
+    }
+    return check_launch();
+}
 
 // ---- one role over the whole block ----------------------------------------------------
 template <class Role, int T, int MINB>
-int launch_solo(typename Role::Args a, int blocks_per_sm, cudaStream_t s) {
+int launch_solo(typename Role::Args a, int blocks_per_sm, cudaStream_t s, bool dependent = false) {
     DeviceFacts f;
     if (int rc = device_facts(f)) return rc;
     auto kern = solo_kernel<Role, T, MINB>;
@@ -91,13 +147,12 @@ int launch_solo(typename Role::Args a, int blocks_per_sm, cudaStream_t s) {
     const int bps = blocks_per_sm > 0 ? blocks_per_sm : resident_blocks((const void*)kern, T, smem);
     const int grid = f.sms * bps;
     if (int rc = Role::plan(a, T, grid)) return rc;
-    kern<<<grid, T, smem, s>>>(a);
-    return check_launch();
+    return launch_kernel(kern, grid, T, smem, s, dependent, a);
 }
 
 // ---- two roles side by side ------------------------------------------------------------
 template <class RA, class RB, int TA, int TB, int MINB>
-int launch_pair(typename RA::Args a, typename RB::Args b, int blocks_per_sm, cudaStream_t s) {
+int launch_pair(typename RA::Args a, typename RB::Args b, int blocks_per_sm, cudaStream_t s, bool dependent = false) {
     DeviceFacts f;
     if (int rc = device_facts(f)) return rc;
     auto kern = fused_kernel<RA, RB, TA, TB, MINB>;
@@ -109,14 +164,14 @@ int launch_pair(typename RA::Args a, typename RB::Args b, int blocks_per_sm, cud
     const int grid = f.sms * bps;
     if (int rc = RA::plan(a, TA, grid)) return rc;
     if (int rc = RB::plan(b, TB, grid)) return rc;
-    kern<<<grid, TA + TB, smem, s>>>(a, b, smem_a);
-    return check_launch();
+    return launch_kernel(kern, grid, TA + TB, smem, s, dependent, a, b, smem_a);
 }
 
 // ---- two roles side by side, the second one taking over a share of the first one's items -----
 // share_permille of role A's items (rounded down to whole rows) go to role B's thread range.
 template <class RA, class RB, int TA, int TB, int MINB>
-int launch_pair_share(typename RA::Args a, typename RB::Args b, int blocks_per_sm, int share_permille, cudaStream_t s) {
+int launch_pair_share(typename RA::Args a, typename RB::Args b, int blocks_per_sm, int share_permille, cudaStream_t s,
+                      bool dependent = false) {
     DeviceFacts f;
     if (int rc = device_facts(f)) return rc;
     auto kern = fused_share_kernel<RA, RB, TA, TB, MINB>;
@@ -135,13 +190,12 @@ int launch_pair_share(typename RA::Args a, typename RB::Args b, int blocks_per_s
         const unsigned long long given = (unsigned long long)items * (unsigned)share_permille / 1000ull;
         split = items - (unsigned)(given / row * row);
     }
-    kern<<<grid, TA + TB, smem, s>>>(a, b, smem_a, split, items);
-    return check_launch();
+    return launch_kernel(kern, grid, TA + TB, smem, s, dependent, a, b, smem_a, split, items);
 }
 
 // ---- the same threads run both roles one after the other (vertical fusion) ------------------
 template <class RA, class RB, int T, int MINB>
-int launch_vpair(typename RA::Args a, typename RB::Args b, int blocks_per_sm, cudaStream_t s) {
+int launch_vpair(typename RA::Args a, typename RB::Args b, int blocks_per_sm, cudaStream_t s, bool dependent = false) {
     DeviceFacts f;
     if (int rc = device_facts(f)) return rc;
     auto kern = vfused_kernel<RA, RB, T, MINB>;
@@ -153,8 +207,7 @@ int launch_vpair(typename RA::Args a, typename RB::Args b, int blocks_per_sm, cu
     const int grid = f.sms * bps;
     if (int rc = RA::plan(a, T, grid)) return rc;
     if (int rc = RB::plan(b, T, grid)) return rc;
-    kern<<<grid, T, smem, s>>>(a, b);
-    return check_launch();
+    return launch_kernel(kern, grid, T, smem, s, dependent, a, b);
 }
 
 // chunk of nonces a warp takes from a queue at a time: about 16 chunks per resident warp,

@@ -94,6 +94,10 @@ class BnExchange:
         _lib.check(_lib.lib().hfuse_exchange_status(self._h, C.byref(flag)), "hfuse_exchange_status")
         return bool(flag.value)
 
+    def clear_status(self, stream=None) -> None:
+        """Lower the timed-out flag again (it stays raised once a wait has run out)."""
+        _lib.check(_lib.lib().hfuse_exchange_clear_status(self._h, _stream_ptr(stream)), "hfuse_exchange_clear_status")
+
     def close(self):
         if self._h:
             if torch.cuda.is_available():

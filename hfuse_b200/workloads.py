@@ -40,9 +40,10 @@ def config0(device=None, batch=16):
             "bytes": batch * (64 * 56 * 56 * 4 * 10 + 64 * 112 * 112 * 4 + 64 * 56 * 56 * 12)}
 
 
-def config1(device=None, bn_batch=32, up_batch=16):
-    """BN statistics [B1,256,28,28] ~ 0.5 + 2.0*randn, eps 1e-5  +  bilinear x2 [B2,128,56,56] U(0,1); seed 1."""
-    torch.manual_seed(1)
+def config1(device=None, bn_batch=32, up_batch=16, seed=1):
+    """BN statistics [B1,256,28,28] ~ 0.5 + 2.0*randn, eps 1e-5  +  bilinear x2 [B2,128,56,56] U(0,1); seed 1.
+    (Another seed gives another draw of the same distributions: the batch shards of a multi-GPU run.)"""
+    torch.manual_seed(seed)
     bn = 0.5 + 2.0 * torch.randn(bn_batch, 256, 28, 28)
     up = torch.rand(up_batch, 128, 56, 56)
     return {"bn": _dev(bn, device), "up": _dev(up, device), "eps": 1e-5,

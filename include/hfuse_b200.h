@@ -46,7 +46,8 @@ enum {
     HFUSE_ERR_LAUNCH = -5,      /* cudaGetLastError() after the launch was not cudaSuccess */
     HFUSE_ERR_NO_DEVICE = -6,   /* no usable sm_100 device */
     HFUSE_ERR_UNKNOWN_PAIR = -7,
-    HFUSE_ERR_NOALLOC_LIMIT = -8 /* more channels than the built-in scratch of the no-allocation entry serves */
+    HFUSE_ERR_NOALLOC_LIMIT = -8, /* more channels than the built-in scratch of the no-allocation entry serves */
+    HFUSE_ERR_COMM = -9          /* NCCL could not be loaded, or one of its calls failed */
 };
 
 HFUSE_API const char* hfuse_error_string(int code);
@@ -123,8 +124,11 @@ HFUSE_API int hfuse_bnstats_finalize_f64(const double* moments, int C, float eps
  * arguments and results as hfuse_bnstats_f32 minus the workspace; the scratch is a static
  * device array inside the library (3,149,824 bytes on every GPU that loads it, held until
  * exit), which limits C to HFUSE_NOALLOC_MAX_CHANNELS (larger C returns
- * HFUSE_ERR_NOALLOC_LIMIT).  The call itself allocates nothing.  The first call on each
- * device looks up the array's address; make that call before any stream capture begins.
+ * HFUSE_ERR_NOALLOC_LIMIT).  The call itself asks no allocator for anything.  The first call
+ * on each device looks up the array's address, and with lazy module loading that is also the
+ * moment the CUDA runtime loads this library's device code onto the device and the driver places
+ * the array: make one warm-up call per device before any stream capture begins and before the
+ * phase in which nothing may be allocated; later calls leave the device's free memory as it is.
  * All calls on a device share the one array: calls that may overlap on the GPU (different
  * streams without ordering between them) race and must be serialised by the caller. */
 #define HFUSE_NOALLOC_MAX_CHANNELS 1024
@@ -192,6 +196,10 @@ HFUSE_API int hfuse_maxpool_backward_bn_backward_f32(
  * last one has arrived.  Rules: every rank makes the same sequence of calls on one exchange
  * object; calls on one object go to one stream; the in-kernel wait for the other ranks gives
  * up after 5 s and raises the flag hfuse_exchange_status reports (results are then invalid).
+ * Which slot of the buffer a call uses is counted on the device, by the kernels themselves, so
+ * the calls may be captured in a CUDA graph and replayed any number of times (every rank must
+ * replay the same number of calls), and a call that returned an error never ran and does not
+ * count.  The status flag stays raised until hfuse_exchange_clear_status.
  * ------------------------------------------------------------------------------------- */
 #define HFUSE_IPC_HANDLE_BYTES 64
 #define HFUSE_MAX_RANKS 8
@@ -208,6 +216,8 @@ HFUSE_API int hfuse_exchange_connect_pointers(hfuse_exchange* ex, void* const* b
 /* limit of the in-kernel wait for the other ranks' moments (default 5 s), for later calls */
 HFUSE_API int hfuse_exchange_set_timeout(hfuse_exchange* ex, uint64_t nanoseconds);
 HFUSE_API int hfuse_exchange_status(hfuse_exchange* ex, int* timed_out);   /* synchronises the device */
+/* lowers the flag again, ordered after the earlier work on `stream` */
+HFUSE_API int hfuse_exchange_clear_status(hfuse_exchange* ex, hfuse_stream_t stream);
 HFUSE_API int hfuse_exchange_destroy(hfuse_exchange* ex);
 HFUSE_API int hfuse_bnstats_allreduce_f32(HFUSE_BNSTATS_PARAMS(), hfuse_exchange* ex, hfuse_stream_t stream);
 HFUSE_API int hfuse_upsample_bnstats_allreduce_f32(HFUSE_UPSAMPLE_PARAMS(a_), HFUSE_BNSTATS_PARAMS(b_),
@@ -242,7 +252,9 @@ HFUSE_API int hfuse_upsample_bnstats_allreduce_f32(HFUSE_UPSAMPLE_PARAMS(a_), HF
  * `count` must start at zero and counts every hit found even beyond HFUSE_MAX_HITS; slots
  * are filled in arrival order, so sort by nonce before comparing.  `reserved` is the work
  * queue cursor of the fused searches (thread ranges take chunks of nonces from it); the
- * fused entry points clear it themselves. */
+ * fused entry points clear it themselves.  The two halves of a fused search need two DIFFERENT
+ * records (one record for both returns HFUSE_ERR_BAD_ARG).  count <= 2^61 (2^32 for the 32-bit
+ * nonces). */
 typedef struct hfuse_hits {
     uint32_t count;
     uint32_t reserved;
@@ -298,6 +310,35 @@ HFUSE_API int hfuse_hash_batch(int kind, const uint8_t* header, const void* dag,
                                hfuse_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Multi-GPU entry points for hosts written in C or C++ (no counterpart in the reference, which
+ * is single-GPU): one process or host thread per GPU, NCCL underneath (loaded at run time from
+ * libnccl.so.2; without it these calls return HFUSE_ERR_COMM and everything else still works).
+ * Rank 0 makes an id (hfuse_comm_unique_id), hands it to the other ranks by any transport, and
+ * every rank calls hfuse_comm_create with its own GPU current (a collective call).
+ *   hfuse_bnstats_allreduce_nccl_f64: sums the [C][3] double moments that hfuse_bnstats_f32 (or a
+ *       pair with it) wrote on every rank, in place, then mean / invstd of the whole batch — the
+ *       library-collective counterpart of the in-kernel exchange above;
+ *   hfuse_histc_allreduce_counts: sums the histogram counts of the batch shards, in place;
+ *   hfuse_dag_broadcast: rank `root` sends its DAG to all others (instead of every rank
+ *       generating its own copy);
+ *   *_search_sharded: the fused search over this rank's contiguous share of both nonce ranges
+ *       (hfuse_shard_range); hits stay in the rank's records, the host merges and sorts them.
+ * ------------------------------------------------------------------------------------- */
+#define HFUSE_COMM_ID_BYTES 128
+typedef struct hfuse_comm hfuse_comm;
+HFUSE_API int hfuse_comm_unique_id(uint8_t id[HFUSE_COMM_ID_BYTES]);
+HFUSE_API int hfuse_comm_create(int world, int rank, const uint8_t id[HFUSE_COMM_ID_BYTES], hfuse_comm** out);
+HFUSE_API int hfuse_comm_destroy(hfuse_comm* comm);
+HFUSE_API int hfuse_bnstats_allreduce_nccl_f64(hfuse_comm* comm, double* moments, int C, float eps, float* mean,
+                                               float* invstd, hfuse_stream_t stream);
+HFUSE_API int hfuse_histc_allreduce_counts(hfuse_comm* comm, uint32_t* counts, int nbins, hfuse_stream_t stream);
+HFUSE_API int hfuse_dag_broadcast(hfuse_comm* comm, void* dag, size_t bytes, int root, hfuse_stream_t stream);
+HFUSE_API int hfuse_blake256_sha256d_search_sharded(HFUSE_BLAKE256_PARAMS(a_), HFUSE_SHA256D_PARAMS(b_), int rank,
+                                                    int world, hfuse_stream_t stream);
+HFUSE_API int hfuse_sia_ethash_search_sharded(HFUSE_SIA_PARAMS(a_), HFUSE_ETHASH_PARAMS(b_), int rank, int world,
+                                              hfuse_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
  * Tuning (the reference sweeps the split in 128-thread steps and a launch-bound register
  * cap per pair, tools/llvm-smart-fuser/main.cpp:182-236; here each pair has a compiled
  * list of (T1, T2, blocks/SM) variants).  `pair` is the entry point's name without the
@@ -311,6 +352,14 @@ HFUSE_API int hfuse_tune_describe(const char* pair, int variant, char* buf, size
  * items that the statistics thread range takes over between sending its moments to the peers and
  * waiting for theirs.  Any other name: HFUSE_ERR_UNKNOWN_PAIR. */
 HFUSE_API int hfuse_tune_set_share(const char* pair, int permille);
+
+/* Named switches between alternative code paths of a kernel (default 0).  Unknown name:
+ * HFUSE_ERR_UNKNOWN_PAIR.
+ *   "im2col_store_path": 0 = the im2col role keeps its patch in registers and writes the taps with
+ *       256-bit streaming stores; 1 = 3x3 / stride 1 / pad 1 shapes go through a shared-memory
+ *       tile and leave as bulk (TMA) copies of whole tap bands.  Same bytes either way; kept as
+ *       a measured alternative (the streaming stores are the faster of the two on B200). */
+HFUSE_API int hfuse_tune_option(const char* name, int value);
 
 /* Host utility (no counterpart in the reference, which is single-GPU): the share of `total` batch
  * items or nonces that rank `rank` of `world` works on, one process per GPU.  Contiguous and

@@ -80,6 +80,19 @@ def test_host_generator_matches_oracle():
     assert int.from_bytes(c3["target"], "big") == 2 ** 224
 
 
+def test_fused_search_needs_two_different_hit_records_and_a_count_that_fits_the_queue():
+    L = _lib.lib()
+    hdr, target = bytes(80), bytes(32)
+    rec, rec2 = 4096, 8192          # never dereferenced: the checks come before any CUDA call
+    assert L.hfuse_blake256_sha256d_search(hdr, 0, 1 << 20, target, rec, hdr, 0, 1 << 20, target, rec, None) == -1
+    assert L.hfuse_blake256_sia_search(hdr, 0, 1 << 20, target, rec, hdr, 0, (1 << 61) + 1, target, rec2, None) == -3
+    assert L.hfuse_blake256_sia_search(hdr, 0, (1 << 32) + 1, target, rec, hdr, 0, 1 << 20, target, rec2, None) == -3
+    assert L.hfuse_exchange_clear_status(None, None) == -1
+    assert L.hfuse_tune_option(b"im2col_store_path", 2) == -1
+    assert L.hfuse_tune_option(b"nothing", 1) == -7
+    assert L.hfuse_tune_option(b"im2col_store_path", 0) == 0
+
+
 def test_ops_refuse_cpu_tensors():
     import pytest
     import torch

@@ -163,6 +163,42 @@ def test_full_nonce_space_sweep_config3(dev):
         OC.search(0, c["blake_header"], 0, 1 << 22, t)[1]
 
 
+def test_config4_on_the_full_dag(dev):
+    """Configuration 4 on its real 1 GiB DAG (2^23 items of xoshiro256** bytes).  The first 2^18
+    nonces with an easy target: hits, mix digests and Sia hits equal the oracle's sweep over the
+    same DAG, fused and standalone.  Then the full 2^30 sweep of the benchmark in one fused launch:
+    every reported hit is re-hashed by the oracle (mix digest equal, result below the boundary) and
+    the hit count is what 2^30 draws at 2^-24 make plausible."""
+    c = workloads.config4()
+    host = c["dag"].numpy()
+    dag = c["dag"].to(dev)
+    assert dag.numel() == 1 << 30
+    easy = crypto.target_from_difficulty_bits(12)
+    n = 1 << 18
+    found, nonces, mixes = OC.search(3, c["header_hash"], 0, n, easy, dag=host)
+    sia_found, sia_nonces = OC.search(2, c["sia_header"], 0, n, easy)
+    assert found > 30 and sia_found > 30
+    s, e = crypto.Sia(c["sia_header"], 0, n, easy), crypto.Ethash(dag, c["header_hash"], 0, n, easy)
+    crypto.run_pair(s, e)
+    total, hits = e.result()
+    assert total == found and [h[0] for h in hits] == nonces and [h[1] for h in hits] == mixes
+    assert s.nonces() == sia_nonces
+    assert crypto.run(crypto.Ethash(dag, c["header_hash"], 0, n, easy)).result() == (total, hits)
+    # the benchmark's own sweep
+    s, e = crypto.Sia(c["sia_header"], c["start"], c["count"], c["target"]), \
+        crypto.Ethash(dag, c["header_hash"], c["start"], c["count"], c["target"])
+    crypto.run_pair(s, e)
+    total, hits = e.result()
+    assert 20 <= total <= 130 and total == len(hits)              # expectation 64
+    for nonce, mix in hits:
+        m, r = OC.hashimoto(host, c["header_hash"], nonce)
+        assert m == mix and r < c["target"]
+    stotal, shits = s.result()
+    assert 20 <= stotal <= 130
+    for nonce, _ in shits:
+        assert OC.sia_header(c["sia_header"], nonce) < c["target"]
+
+
 def test_dag_generation_matches_oracle_and_feeds_the_search(dev):
     """Light cache on the host, DAG nodes on the GPU, then a search over the generated DAG."""
     seed = workloads.xoshiro_bytes(55, 32).tobytes()

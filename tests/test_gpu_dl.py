@@ -160,6 +160,36 @@ def test_histc_shapes(dev, n, nb, lo, hi):
     assert np.array_equal(got, dl.histc_numpy(x.numpy(), nb, lo, hi))
 
 
+def test_histc_edge_values_ragged_sizes_and_dirty_counts_for_every_variant(dev):
+    """Values at and next to both bounds, infinities and NaN; sizes around the boundaries of the
+    sweep's unchecked main loop (one group = 4 items x threads x blocks); and a counts buffer that
+    holds garbage before every call (the entry point clears it on the stream, with a kernel the
+    histogram kernel only waits for before its flush)."""
+    g = torch.Generator().manual_seed(160)
+    f32 = np.float32
+    group = 148 * 1024 * 4 * 4
+    for nb, lo, hi in ((256, -4.0, 4.0), (100, -3.0, 2.5), (7, 0.1, 0.7), (1000, -1.0, 3.0)):
+        edges = [lo, hi, np.nextafter(f32(lo), f32(-np.inf)), np.nextafter(f32(lo), f32(np.inf)),
+                 np.nextafter(f32(hi), f32(-np.inf)), np.nextafter(f32(hi), f32(np.inf)),
+                 float("inf"), -float("inf"), float("nan"), -0.0, 0.0]
+        for n in (11, 4 * 1024 + 1, group - 4, group, group + 7, 2 * group + 4 * 77 + 3):
+            x = torch.randn(n, generator=g) * 1.5
+            x[:len(edges)] = torch.tensor([float(e) for e in edges])
+            want = dl.histc_numpy(x.numpy(), nb, lo, hi)
+            xd = x.to(dev)
+            op = ops.Histc(xd, nb, lo, hi)
+            for v in range(len(_lib.tune_variants("histc"))):
+                _lib.tune_set("histc", v, 0)
+                try:
+                    op.counts.fill_(-7)
+                    assert np.array_equal(_u32(ops.run(op)), want), (nb, lo, hi, n, v)
+                finally:
+                    _lib.tune_set("histc", -1, 0)
+            # two calls in a row into the same buffer: the second must not see the first's counts
+            ops.run(op)
+            assert np.array_equal(_u32(ops.run(op)), want)
+
+
 def test_full_size_configurations(dev):
     w = workloads.config0()
     col = ops.im2col(w["im"].to(dev), **w["im2col"])
@@ -193,6 +223,50 @@ def test_every_standalone_variant_gives_the_same_bytes(dev):
             assert torch.equal(ops.im2col(x, 3, 1, 1, 1), base)
         finally:
             _lib.tune_set("im2col", -1, 0)
+
+
+def test_im2col_through_shared_memory_and_bulk_stores_gives_the_same_bytes(dev):
+    """The alternative store path (option im2col_store_path = 1): 3x3 / stride 1 / pad 1 shapes go
+    through a shared-memory tile and bulk copies; every other shape must keep its usual path."""
+    g = torch.Generator().manual_seed(19)
+    cases = [((2, 3, 12, 16), (3, 3, 1, 1, 1, 1, 1, 1)),     # one band per plane
+             ((1, 2, 64, 56), (3, 3, 1, 1, 1, 1, 1, 1)),     # several bands, ragged last band
+             ((3, 1, 1, 4), (3, 3, 1, 1, 1, 1, 1, 1)),       # a single row
+             ((1, 1, 5, 2048), (3, 3, 1, 1, 1, 1, 1, 1)),    # rows too wide for the tile: usual path
+             ((2, 2, 10, 8), (3, 3, 2, 2, 1, 1, 1, 1)),      # pad 2: usual path
+             ((1, 2, 9, 11), (5, 2, 2, 1, 2, 3, 1, 2))]      # generic path
+    try:
+        _lib.tune_option("im2col_store_path", 1)
+        for shape, prm in cases:
+            x = torch.rand(*shape, generator=g) * 2 - 1
+            kh, kw, ph, pw, sh, sw, dh, dw = prm
+            want = dl.im2col_torch(x, *prm)
+            for v in range(len(_lib.tune_variants("im2col"))):
+                _lib.tune_set("im2col", v, 0)
+                out = ops.im2col(x.to(dev), (kh, kw), (ph, pw), (sh, sw), (dh, dw))
+                assert torch.equal(out.cpu(), want), (shape, prm, v)
+            _lib.tune_set("im2col", -1, 0)
+        # the benchmark shape, alone and fused with max-pool (another role beside it in the block)
+        w = workloads.config0(batch=4)
+        a = ops.Im2col(w["im"].to(dev), **w["im2col"])
+        b = ops.MaxPool(w["pool"].to(dev), **w["maxpool"])
+        want = dl.im2col_torch(w["im"], 3, 3, 1, 1, 1, 1, 1, 1)
+        ops.run(a)
+        assert torch.equal(a.out.cpu(), want)
+        a.out.zero_()
+        ops.run_pair(a, b)
+        assert torch.equal(a.out.cpu(), want)
+        vr, ir = dl.maxpool_torch(w["pool"], 2, 2, 2, 2, 0, 0, 1, 1)
+        assert torch.equal(b.out.cpu(), vr) and torch.equal(b.idx.cpu(), ir)
+        h = ops.Histc(torch.randn(100000, generator=g).to(dev), 256, -4.0, 4.0)      # 32 KB more shared memory
+        a.out.zero_()
+        ops.run_pair(a, h)
+        assert torch.equal(a.out.cpu(), want)
+    finally:
+        _lib.tune_option("im2col_store_path", 0)
+        _lib.tune_set("im2col", -1, 0)
+    with pytest.raises(_lib.HfuseError):
+        _lib.tune_option("no_such_option", 1)
 
 
 def test_error_codes_on_device_buffers(dev):

@@ -144,6 +144,149 @@ def test_a_rank_that_never_arrives_ends_the_wait_with_a_status_and_the_late_rank
         ex1.close()
 
 
+def test_fused_exchange_pair_across_two_ranks_launched_one_after_the_other(dev):
+    """The fused pair (upsample | statistics: send, share of the upsample, collect) with two ranks
+    driven by this process on one GPU.  Rank 0 runs alone: its collect runs out of time (20 ms)
+    and raises the status, but its upsample, including the share handed to the statistics thread
+    range, is complete and bit-exact.  Rank 1 then finds rank 0's rows, does not wait, and reports
+    the statistics of both batches.  The two launches never wait on each other at the same time."""
+    from hfuse_b200 import _lib
+    from hfuse_b200.exchange import BnExchange
+    g = torch.Generator().manual_seed(92)
+    for C, shape in ((24, (8, 24, 10, 10)), (256, (4, 256, 28, 28))):       # few channels; one channel per block
+        x = 0.5 + 2.0 * torch.randn(*shape, generator=g)
+        mr, sr = dl.bnstats_f64(x, 1e-5)
+        half = shape[0] // 2
+        up0, up1 = torch.rand(2, 5, 12, 16, generator=g), torch.rand(3, 4, 8, 8, generator=g)
+        ex0, ex1 = BnExchange.local_ranks(C, [dev, dev])
+        try:
+            for variant, share in ((-1, -1), (21, 400), (0, 1000)):
+                _lib.tune_set("upsample_bnstats_allreduce", variant, 0)
+                _lib.tune_set_share("upsample_bnstats_allreduce", share)
+                for ex in (ex0, ex1):
+                    ex.set_timeout(0.02)
+                    ex.clear_status()
+                a0, b0 = ops.Upsample(up0.to(dev), scale_factor=2), ops.BnStats(x[:half].contiguous().to(dev), 1e-5)
+                a1, b1 = ops.Upsample(up1.to(dev), scale_factor=2), ops.BnStats(x[half:].contiguous().to(dev), 1e-5)
+                a0.out.fill_(float("nan"))
+                a1.out.fill_(float("nan"))
+                ex0.run_pair(a0, b0)
+                torch.cuda.synchronize()
+                assert ex0.timed_out() and not ex1.timed_out()
+                assert np.array_equal(a0.out.cpu().numpy(), dl.upsample_numpy(up0.numpy(), 24, 32))
+                ex1.run_pair(a1, b1)
+                torch.cuda.synchronize()
+                assert not ex1.timed_out()
+                assert np.array_equal(a1.out.cpu().numpy(), dl.upsample_numpy(up1.numpy(), 16, 16))
+                np.testing.assert_allclose(b1.mean.cpu().double().numpy(), mr.numpy(), rtol=1e-5)
+                np.testing.assert_allclose(b1.invstd.cpu().double().numpy(), sr.numpy(), rtol=1e-5)
+        finally:
+            _lib.tune_set("upsample_bnstats_allreduce", -1, 0)
+            _lib.tune_set_share("upsample_bnstats_allreduce", -1)
+            ex0.close()
+            ex1.close()
+
+
+def test_calls_replayed_from_a_cuda_graph_move_on_to_the_next_slot_and_epoch(dev):
+    """Slot and epoch of a call are counted on the device, so a captured call that is replayed
+    does not meet the rows of its previous replay.  World of one: three replays of ONE captured
+    call follow three different inputs.  Two ranks on one GPU, one captured call each, replayed
+    one after the other: on every replay rank 0 (alone at that moment) must run out of time again
+    instead of folding the row rank 1 left in the previous replay, and rank 1 must report the
+    statistics of the inputs of THIS replay."""
+    from hfuse_b200.exchange import BnExchange
+    g = torch.Generator().manual_seed(93)
+    shape = (8, 24, 10, 10)
+    xs = [0.5 * k + (1.0 + k) * torch.randn(*shape, generator=g) for k in range(3)]
+    side = torch.cuda.Stream(dev)
+    # ---- world of one
+    ex = BnExchange(24)
+    try:
+        buf = xs[0].to(dev)
+        op = ops.BnStats(buf, 1e-5)
+        up = torch.rand(2, 3, 8, 8, generator=g)
+        a = ops.Upsample(up.to(dev), scale_factor=2)
+        with torch.cuda.stream(side):
+            ex.run_pair(a, op)                                   # warm-up outside the capture
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
+                ex.run_pair(a, op)
+        for x in xs + xs:                                        # six replays: every slot is reused
+            buf.copy_(x)
+            graph.replay()
+            torch.cuda.synchronize()
+            mr, sr = dl.bnstats_f64(x, 1e-5)
+            np.testing.assert_allclose(op.mean.cpu().double().numpy(), mr.numpy(), rtol=1e-5)
+            np.testing.assert_allclose(op.invstd.cpu().double().numpy(), sr.numpy(), rtol=1e-5)
+        assert not ex.timed_out()
+        del graph
+    finally:
+        ex.close()
+    # ---- two ranks, sequential
+    ex0, ex1 = BnExchange.local_ranks(24, [dev, dev])
+    try:
+        for e in (ex0, ex1):
+            e.set_timeout(0.02)
+        buf0, buf1 = xs[0][:4].contiguous().to(dev), xs[0][4:].contiguous().to(dev)
+        b0, b1 = ops.BnStats(buf0, 1e-5), ops.BnStats(buf1, 1e-5)
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
+                ex0.run(b0)
+                ex1.run(b1)
+        for x in xs + xs:
+            buf0.copy_(x[:4])
+            buf1.copy_(x[4:])
+            ex0.clear_status()
+            torch.cuda.synchronize()
+            graph.replay()
+            torch.cuda.synchronize()
+            assert ex0.timed_out()            # rank 1's row of THIS call was not there yet
+            assert not ex1.timed_out()
+            mr, sr = dl.bnstats_f64(x, 1e-5)
+            np.testing.assert_allclose(b1.mean.cpu().double().numpy(), mr.numpy(), rtol=1e-5)
+            np.testing.assert_allclose(b1.invstd.cpu().double().numpy(), sr.numpy(), rtol=1e-5)
+        del graph
+    finally:
+        ex0.close()
+        ex1.close()
+
+
+def test_a_call_that_fails_on_the_host_does_not_put_the_rank_out_of_step(dev):
+    """A call refused after its arguments were accepted (here: a sliced plan without scratch) never
+    ran, so it must not count as a use of the exchange: the next good call of that rank has to meet
+    its peer in the same slot with the same epoch."""
+    from hfuse_b200 import _lib
+    from hfuse_b200.exchange import BnExchange
+    g = torch.Generator().manual_seed(94)
+    x = 0.5 + 2.0 * torch.randn(64, 4, 32, 32, generator=g)         # few channels: cut into slices, needs scratch
+    mr, sr = dl.bnstats_f64(x, 1e-5)
+    ex0, ex1 = BnExchange.local_ranks(4, [dev, dev])
+    try:
+        for e in (ex0, ex1):
+            e.set_timeout(0.02)
+        bad = ops.BnStats(x[:32].contiguous().to(dev), 1e-5, workspace=torch.zeros(16, dtype=torch.uint8, device=dev))
+        with pytest.raises(_lib.HfuseError) as err:
+            ex0.run(bad)
+        assert err.value.code == -4
+        b0 = ops.BnStats(x[:32].contiguous().to(dev), 1e-5)
+        b1 = ops.BnStats(x[32:].contiguous().to(dev), 1e-5, workspace=torch.zeros_like(b0.ws))
+        ex0.run(b0)                            # alone: runs out of time, but its rows are delivered
+        ex1.run(b1)
+        torch.cuda.synchronize()
+        assert not ex1.timed_out()
+        np.testing.assert_allclose(b1.mean.cpu().double().numpy(), mr.numpy(), rtol=1e-5)
+        np.testing.assert_allclose(b1.invstd.cpu().double().numpy(), sr.numpy(), rtol=1e-5)
+        # the flag stays up until it is cleared
+        assert ex0.timed_out()
+        ex0.clear_status()
+        assert not ex0.timed_out()
+    finally:
+        ex0.close()
+        ex1.close()
+
+
 def _rank_main(rank, world, port, ret):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)

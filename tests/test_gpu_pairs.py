@@ -88,6 +88,20 @@ def test_pair_config1_against_oracle(dev):
     np.testing.assert_allclose(b.invstd.cpu().double().numpy(), sr.numpy(), rtol=1e-5)
 
 
+def test_pair_config2_at_full_size_against_oracle(dev):
+    """Configuration 2 as the benchmark runs it: im2col of batch 32 fused with histc over 2^24 values."""
+    w = workloads.config2()
+    assert w["im"].shape[0] == 32 and w["hist"].numel() == 1 << 24
+    a = ops.Im2col(w["im"].to(dev), **w["im2col"])
+    b = ops.Histc(w["hist"].to(dev), w["bins"], w["lo"], w["hi"])
+    b.counts.fill_(-3)                                 # the entry point clears the counts itself
+    ops.run_pair(a, b)
+    assert np.array_equal(b.counts.cpu().numpy().view(np.uint32), dl.histc_torch(w["hist"], 256, -4, 4))
+    assert np.array_equal(b.counts.cpu().numpy().view(np.uint32), dl.histc_numpy(w["hist"].numpy(), 256, -4.0, 4.0))
+    ref_col = dl.im2col_torch(w["im"], 3, 3, 1, 1, 1, 1, 1, 1)
+    assert torch.equal(a.out.cpu(), ref_col)
+
+
 def test_pair_config2_against_oracle_and_batch_sharding(dev):
     from hfuse_b200 import sharding
     w = workloads.config2(n_hist=1 << 22, batch=8)
