@@ -16,7 +16,8 @@ with the roofline fraction.
 
 Timing: the K steps of one pass are replayed from a CUDA graph; the timed region is R
 such passes (R chosen so that the region lasts about a second, at least 50), every pass
-bracketed by CUDA events on the launching stream, barrier + synchronize on both sides of
+bracketed by CUDA events on the launching stream (for small K several passes share one
+graph, with event-record nodes between them), barrier + synchronize on both sides of
 the region, every pass's time the max over ranks, the median pass reported (min, max and
 mean beside it).  The steps rotate over several independent buffer sets whose combined
 footprint is several times the L2, so no step finds its inputs in cache.  After the timed
@@ -469,8 +470,8 @@ def check_headline(torch, sets, w, ex, dev, world):
 # an isolated launch (dram__bytes_read.sum + dram__bytes_write.sum).  Both are below the
 # algorithmic 154,142,720 B because about half of the output is still dirty in L2 when an
 # isolated launch ends; the reads (51.7 MB for 51.4 MB of input) show that nothing is read twice.
-NCU_TRAFFIC_BYTES = {"fused_kernel<UpsampleRole,BnStatsRole,512,256,2>": 101_030_656,
-                     "fused_share_kernel<UpsampleRole,BnStatsXchgRole>": 100_900_000}
+NCU_TRAFFIC_BYTES = {"fused_kernel<UpsampleRole,BnStatsRole,512,256,2>": 101_843_456,
+                     "fused_share_kernel<UpsampleRole,BnStatsXchgRole>": 99_475_460}
 
 
 def run_ours(args):
@@ -493,8 +494,8 @@ def run_ours(args):
     _lib.lib()   # fail loudly if the CUDA library is missing
     peak, peak_kind = measured_peak_gbs()
 
-    if args.im2col_path == "bulk":
-        _lib.tune_option("im2col_store_path", 1)
+    if args.im2col_path != "default":
+        _lib.tune_option("im2col_store_path", 1 if args.im2col_path == "bulk" else 0)
     if args.only:
         return run_only(args, torch, ops, crypto, workloads, dev)
     if args.tune:
@@ -572,6 +573,7 @@ def run_ours(args):
     K = args.steps
     G = min(K, 240)
     graphs = []
+    big = None                      # one graph holding P passes with an event between passes
     launch_mode = "direct launches"
     with torch.cuda.stream(stream):
         for i in range(max(args.warmup, NSETS)):
@@ -612,20 +614,53 @@ def run_ours(args):
             import torch.distributed as dist
             dist.all_reduce(est, op=dist.ReduceOp.MAX)       # every rank must choose the same R
         R = int(min(max(50, -(-args.region_ms // est.item())), 20000))
+        # Short passes (small K) are chained: P passes go into ONE graph with an event-record node
+        # between passes, so that a pass does not begin with the host's graph-launch latency (which
+        # every rank would see at a slightly different moment).  The events are read after every
+        # replay of that graph.
+        P = max(1, min(50, 1000 // K)) if graphs and K % G == 0 and K == G else 1
+        pass_ev = None
+        if P > 1:
+            try:
+                pass_ev = [torch.cuda.Event(enable_timing=True, external=True) for _ in range(P + 1)]
+                big = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(big, stream=stream, capture_error_mode="thread_local"):
+                    pass_ev[0].record()
+                    for p_ in range(P):
+                        for i in range(K):
+                            step(p_ * K + i)
+                        pass_ev[p_ + 1].record()
+                big.replay()
+                stream.synchronize()
+                pass_ev[0].elapsed_time(pass_ev[1])          # raises if such events cannot be timed
+                R = -(-R // P) * P
+                launch_mode = f"CUDA graph of {P} passes x {K} steps with an event node between passes, replayed"
+            except Exception as exc:
+                sys.stderr.write(f"event nodes inside a graph unavailable ({exc!r}); one graph launch per pass\n")
+                big, pass_ev, P = None, None, 1
+                torch.cuda.synchronize()
         sampler = ClockSampler(local)
         sampler.start()       # before the barrier: starting it takes a variable time on every rank
         torch.cuda.synchronize()
         barrier()
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(R + 1)]
-        ev[0].record()
-        for r in range(R):
-            one_pass()
-            ev[r + 1].record()
-        stream.synchronize()
+        pass_ms = []
+        if big is not None:
+            for _ in range(R // P):
+                big.replay()
+                stream.synchronize()
+                pass_ms += [pass_ev[p_].elapsed_time(pass_ev[p_ + 1]) for p_ in range(P)]
+        else:
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(R + 1)]
+            ev[0].record()
+            for r in range(R):
+                one_pass()
+                ev[r + 1].record()
+            stream.synchronize()
+            pass_ms = [ev[r].elapsed_time(ev[r + 1]) for r in range(R)]
     torch.cuda.synchronize()
     barrier()
     clocks = sampler.stop()
-    passes = torch.tensor([ev[r].elapsed_time(ev[r + 1]) for r in range(R)], dtype=torch.float64, device=dev)
+    passes = torch.tensor(pass_ms, dtype=torch.float64, device=dev)
     if use_dist:
         import torch.distributed as dist
         dist.all_reduce(passes, op=dist.ReduceOp.MAX)
@@ -657,6 +692,18 @@ def run_ours(args):
         _lib.check(_lib.lib().hfuse_hbm_probe(None, 0, pdst[i % NSETS].data_ptr(), wr,
                                               torch.cuda.current_stream().cuda_stream), "hfuse_hbm_probe")
     t_wr = graph_region(torch, probe_w, NSETS, 120, 3)
+    # and both again with the writes issued as bulk (TMA) copies of 8 KB from shared memory
+    wr_b = wr // 8192 * 8192
+
+    def probe_b(i):
+        _lib.check(_lib.lib().hfuse_hbm_probe_bulk(psrc[i % NSETS].data_ptr(), rd, pdst[i % NSETS].data_ptr(), wr_b,
+                                                   torch.cuda.current_stream().cuda_stream), "hfuse_hbm_probe_bulk")
+    t_mix_b = graph_region(torch, probe_b, NSETS, 120, 3)
+
+    def probe_wb(i):
+        _lib.check(_lib.lib().hfuse_hbm_probe_bulk(None, 0, pdst[i % NSETS].data_ptr(), wr_b,
+                                                   torch.cuda.current_stream().cuda_stream), "hfuse_hbm_probe_bulk")
+    t_wr_b = graph_region(torch, probe_wb, NSETS, 120, 3)
     del psrc, pdst
 
     # ---- end to end through the C ABI with host buffers (pinned), copies inside the timed region
@@ -763,7 +810,9 @@ def run_ours(args):
                      "kernel_us_source": "the timed region: its only launches are this kernel",
                      "same_bytes_memcpy_d2d_us": round(t_copy * 1e3, 2),
                      "same_read_write_mix_bare_kernel_us": round(t_mix * 1e3, 2),
-                     "write_only_bare_kernel_gbs": round(wr / t_wr / 1e6, 1)},
+                     "write_only_bare_kernel_gbs": round(wr / t_wr / 1e6, 1),
+                     "same_read_write_mix_bulk_store_kernel_us": round(t_mix_b * 1e3, 2),
+                     "write_only_bulk_store_kernel_gbs": round(wr_b / t_wr_b / 1e6, 1)},
         "clocks": clocks,
     }
     if use_dist and not args.no_extras:
@@ -781,7 +830,7 @@ def run_ours(args):
         print(json.dumps(line), flush=True)
     if use_dist:
         wait_for_rank0(rank)
-        shutdown(torch, graphs)
+        shutdown(torch, (graphs, big))
 
 
 def wait_for_rank0(rank):
@@ -800,8 +849,8 @@ def dl_sharded(torch, ops, sharding, workloads, dev, rank, world, barrier, peak)
     """Configuration 2 split over the ranks (strong scaling: the total work is fixed): the im2col
     batch of 32 and the 2^24 histogram values are cut into one contiguous shard per GPU, every rank
     runs the fused im2col + histc pair on its shard, and the 256 counts are summed over ranks with
-    an NCCL all-reduce on the same stream.  Time = max over ranks of the device time per step
-    (fused launch + all-reduce, replayed from a CUDA graph); the results are compared with the
+    an NCCL all-reduce on a side stream (it runs under the next step's kernel).  Time = max over
+    ranks of the device time per step (replayed from a CUDA graph); the results are compared with the
     oracle on the unsplit inputs outside the timed region."""
     import numpy as np
     import torch.distributed as dist
@@ -811,21 +860,39 @@ def dl_sharded(torch, ops, sharding, workloads, dev, rank, world, barrier, peak)
     im = sharding.shard_batch(w["im"], rank, world).contiguous()
     hv = sharding.shard_flat(w["hist"], rank, world).contiguous()
     sets = [(ops.Im2col(im.to(dev), **w["im2col"]), ops.Histc(hv.to(dev), w["bins"], w["lo"], w["hi"])) for _ in range(NS)]
-    stream = torch.cuda.Stream(dev)
+    stream, side = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    summed = [None] * NS          # per buffer set: its counts have been summed (they may be cleared again)
 
     def step(i):
-        a, b = sets[i % NS]
+        # the all-reduce of step i runs on a side stream under the kernel of step i + 1
+        k = i % NS
+        a, b = sets[k]
+        if summed[k] is not None:
+            torch.cuda.current_stream().wait_event(summed[k])
         ops.run_pair(a, b)
-        sharding.allreduce_counts(b.counts)
+        done = torch.cuda.Event()
+        done.record()
+        with torch.cuda.stream(side):
+            side.wait_event(done)
+            sharding.allreduce_counts(b.counts)
+            summed[k] = torch.cuda.Event()
+            summed[k].record()
+
+    def join():
+        torch.cuda.current_stream().wait_stream(side)
     with torch.cuda.stream(stream):
         for i in range(2 * NS):
             step(i)
+        join()
         stream.synchronize()
+        summed = [None] * NS
         G = 6 * NS
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
             for i in range(G):
                 step(i)
+            join()
+        summed = [None] * NS      # events recorded during capture must not be waited on outside
         graph.replay()
         stream.synchronize()
         barrier()
@@ -851,7 +918,7 @@ def dl_sharded(torch, ops, sharding, workloads, dev, rank, world, barrier, peak)
     return {"workload": f"config 2 split over {world} GPUs: im2col batch {im.shape[0]} and {hv.numel()} histogram values per GPU",
             "scaling": "strong", "us_per_step": round(us, 2), "GB_per_s_total": round(CFG2_BYTES / us / 1e3, 1),
             "frac_of_hbm_peak_per_gpu": round(CFG2_BYTES / world / us / 1e3 / peak, 3),
-            "collective": "NCCL all-reduce of the 256 uint32 counts on the launching stream",
+            "collective": "NCCL all-reduce of the 256 uint32 counts on a side stream, under the next step's kernel",
             "parity_ok": bool(flag.item())}
 
 
@@ -969,23 +1036,41 @@ def shutdown(torch, graph):
 
 
 def run_only(args, torch, ops, crypto, workloads, dev):
-    """One kernel or pair on its benchmark configuration, for profiling:
-    --only cfg0|cfg1|cfg2|cfg3|cfg4|histc_maxpool|histc_upsample|histc_bnstats --mode fused|b2b|a|b [--graph]; cfg1 also takes --mode xchg, the
-    exchange pair (send, share of the upsample, collect) over a world of one."""
+    """One kernel or pair on its benchmark workload, for profiling and store-path comparisons:
+    --only cfg0..cfg4 | any pair name (im2col_bnstats, histc_maxpool, sha256d_ethash, ...)
+    --mode fused|b2b|a|b [--graph].  cfg0/1/2 = im2col_maxpool / upsample_bnstats / im2col_histc,
+    cfg3/4 = blake256_sha256d / sia_ethash.  The halves of the other pairs take the shapes they
+    have in the configuration that names them (im2col at batch 16 except beside histc).  cfg1 also
+    takes --mode xchg: the exchange pair (send, share of the upsample, collect) over a world of one."""
+    if "," in args.only or ":" in args.only:
+        # several items in one process ("cfg0:a,cfg0:b,im2col_bnstats:fused"): one profiler run covers them all
+        for item in args.only.split(","):
+            sub = argparse.Namespace(**vars(args))
+            sub.only, _, mode = item.partition(":")
+            sub.mode = mode or args.mode
+            run_only(sub, torch, ops, crypto, workloads, dev)
+            torch.cuda.empty_cache()
+        return
+    from hfuse_b200 import _lib
     barrier = lambda: None
-    hist_pair = args.only.startswith("histc_")
-    cfg = 2 if hist_pair else int(args.only[-1])
-    if cfg <= 2:
-        if hist_pair:       # the three histc pairs named besides configuration 2: histc_maxpool|upsample|bnstats
-            w0, w1, w2 = workloads.config0(), workloads.config1(), workloads.config2()
-            name, sets = args.only, []
-            for _ in range(2):
-                other = {"histc_maxpool": lambda: ops.MaxPool(w0["pool"].to(dev), **w0["maxpool"]),
-                         "histc_upsample": lambda: ops.Upsample(w1["up"].to(dev), scale_factor=2),
-                         "histc_bnstats": lambda: ops.BnStats(w1["bn"].to(dev), w1["eps"])}[args.only]()
-                sets.append((ops.Histc(w2["hist"].to(dev), w2["bins"], w2["lo"], w2["hi"]), other))
-        else:
-            name, sets, nbytes = build_dl_sets(torch, ops, workloads, cfg, dev, 2)
+    alias = {"cfg0": "im2col_maxpool", "cfg1": "upsample_bnstats", "cfg2": "im2col_histc",
+             "cfg3": "blake256_sha256d", "cfg4": "sia_ethash"}
+    name = alias.get(args.only, args.only)
+    if name in _lib.DL_PAIRS:
+        w0, w1, w2 = workloads.config0(), workloads.config1(), workloads.config2()
+
+        def mk(key):
+            if key == "im2col":
+                return ops.Im2col((w2 if name == "im2col_histc" else w0)["im"].to(dev), **w0["im2col"])
+            if key == "maxpool":
+                return ops.MaxPool(w0["pool"].to(dev), **w0["maxpool"])
+            if key == "bnstats":
+                return ops.BnStats(w1["bn"].to(dev), w1["eps"])
+            if key == "upsample":
+                return ops.Upsample(w1["up"].to(dev), scale_factor=2)
+            return ops.Histc(w2["hist"].to(dev), w2["bins"], w2["lo"], w2["hi"])
+        ka, kb = _lib.DL_PAIRS[name]
+        sets = [(mk(ka), mk(kb)) for _ in range(2)]
         if args.mode == "xchg":
             from hfuse_b200.exchange import BnExchange
             ex = BnExchange(sets[0][1].x.shape[1])
@@ -999,19 +1084,28 @@ def run_only(args, torch, ops, crypto, workloads, dev):
             ms = time_region(torch, fn, args.steps, args.warmup, barrier) / args.steps
         print(json.dumps({"only": name, "mode": args.mode, "us_per_step": round(ms * 1e3, 2)}))
         return
+    if name not in _lib.CRYPTO_PAIRS:
+        raise SystemExit(f"--only {args.only}: not a configuration or a pair name")
     count = args.count
-    if cfg == 3:
-        c = workloads.config3()
-        a = crypto.Blake256(c["blake_header"], 0, count, c["target"])
-        b = crypto.Sha256d(c["sha_header"], 0, count, c["target"])
-    else:
-        c = workloads.config4(dev, dag_items=args.dag_items)
-        a = crypto.Sia(c["sia_header"], 0, count, c["target"])
-        b = crypto.Ethash(c["dag"], c["header_hash"], 0, count, c["target"])
+    c3 = workloads.config3()
+    c4 = None
+    if "ethash" in name or "sia" in name:      # the Sia header comes from configuration 4; only ethash needs its DAG
+        c4 = workloads.config4(dev, dag_items=args.dag_items if "ethash" in name else 1024)
+
+    def mkc(key):
+        if key == "blake256":
+            return crypto.Blake256(c3["blake_header"], 0, count, c3["target"])
+        if key == "sha256d":
+            return crypto.Sha256d(c3["sha_header"], 0, count, c3["target"])
+        if key == "sia":
+            return crypto.Sia(c4["sia_header"], 0, count, c4["target"])
+        return crypto.Ethash(c4["dag"], c4["header_hash"], 0, count, c4["target"])
+    ka, kb = _lib.CRYPTO_PAIRS[name]
+    a, b = mkc(ka), mkc(kb)
     fn = {"fused": lambda i: crypto.run_pair(a, b), "b2b": lambda i: crypto.run_back_to_back(a, b),
           "a": lambda i: crypto.run(a), "b": lambda i: crypto.run(b)}[args.mode]
     ms = time_region(torch, fn, args.steps, args.warmup, barrier) / args.steps
-    print(json.dumps({"only": args.only, "mode": args.mode, "count": count, "ms_per_step": round(ms, 3)}))
+    print(json.dumps({"only": name, "mode": args.mode, "count": count, "ms_per_step": round(ms, 3)}))
 
 
 def run_tune(args, torch, ops, crypto, workloads, dev):
@@ -1037,33 +1131,59 @@ def run_tune(args, torch, ops, crypto, workloads, dev):
 
     result = {"solo": {}, "pair": {}}
     steps = 48
+
+    def paths_of(name):
+        """Store paths of the im2col role to sweep for this kernel or pair (others have one)."""
+        return (0, 1) if "im2col" in name else (None,)
+
+    def sweep(name, run_one):
+        """{(path, variant description): us} over every store path and compiled variant."""
+        times = {}
+        try:
+            for path in paths_of(name):
+                if path is not None:
+                    _lib.tune_option("im2col_store_path", path)
+                for v, d in enumerate(_lib.tune_variants(name)):
+                    _lib.tune_set(name, v, 0)
+                    times[(path, d)] = round(graph_region(torch, run_one, NS, steps, 3) * 1e3, 2)
+        finally:
+            _lib.tune_option("im2col_store_path", -1)
+            _lib.tune_set(name, -1, 0)
+        return times
+
+    def describe(times, name, horizontal_only):
+        descr = _lib.tune_variants(name)
+        cand = {k: t for k, t in times.items() if not (horizontal_only and ":0:" in k[1])}
+        (path, d), us = min(cand.items(), key=lambda kv: kv[1])
+        out = {"best": descr.index(d), "variant": d, "us": us,
+               "all": {(d2 if p is None else f"{d2} path{p}"): t for (p, d2), t in times.items()}}
+        if path is not None:
+            out["im2col_bulk"] = path
+        return out, path
+
     for key in _lib.DL_SOLO:
         sets = [mk(key) for _ in range(NS)]
-        times = {}
-        for v, d in enumerate(_lib.tune_variants(key)):
-            _lib.tune_set(key, v, 0)
-            times[d] = round(graph_region(torch, lambda i: ops.run(sets[i % NS]), NS, steps, 3) * 1e3, 2)
-        best = min(times, key=times.get)
-        _lib.tune_set(key, list(times).index(best), 0)       # keep the best standalone for the b2b baseline
-        result["solo"][key] = {"best": list(times).index(best), "variant": best, "us": times[best], "all": times}
+        times = sweep(key, lambda i: ops.run(sets[i % NS]))
+        out, path = describe(times, key, False)
+        result["solo"][key] = out
+        _lib.tune_set(key, out["best"], 0)       # keep the best standalone for the b2b baseline
+        if path is not None:
+            solo_im2col_path = path
         del sets
         torch.cuda.empty_cache()
     for name, (ka, kb) in _lib.DL_PAIRS.items():
         big = name == "im2col_histc"
         sets = [(mk(ka, big), mk(kb, big)) for _ in range(NS)]
+        if "im2col" in name:                     # the baseline's standalone im2col takes ITS best path
+            _lib.tune_option("im2col_store_path", solo_im2col_path)
         t_b2b = graph_region(torch, lambda i: ops.run_back_to_back(*sets[i % NS]), NS, steps, 3) * 1e3
-        times = {}
-        for v, d in enumerate(_lib.tune_variants(name)):
-            _lib.tune_set(name, v, 0)
-            times[d] = round(graph_region(torch, lambda i: ops.run_pair(*sets[i % NS]), NS, steps, 3) * 1e3, 2)
-        _lib.tune_set(name, -1, 0)
-        horiz = {d: t for d, t in times.items() if ":0:" not in d}      # "T:0:mb" = vertical fusion
-        vert = {d: t for d, t in times.items() if ":0:" in d}
-        best = min(horiz, key=horiz.get)
-        result["pair"][name] = {"best": list(times).index(best), "variant": best, "us": times[best],
-                                "back_to_back_us": round(t_b2b, 2), "speedup": round(t_b2b / times[best], 3),
-                                "vertical_best": min(vert, key=vert.get), "vertical_us": min(vert.values()),
-                                "all": times}
+        times = sweep(name, lambda i: ops.run_pair(*sets[i % NS]))
+        out, _ = describe(times, name, True)
+        vert = {k: t for k, t in times.items() if ":0:" in k[1]}
+        vbest = min(vert, key=vert.get)
+        out.update({"back_to_back_us": round(t_b2b, 2), "speedup": round(t_b2b / out["us"], 3),
+                    "vertical_best": vbest[1], "vertical_us": vert[vbest]})
+        result["pair"][name] = out
         del sets
         torch.cuda.empty_cache()
     if args.tune_skip_crypto:
@@ -1129,9 +1249,13 @@ def run_study(args, torch, ops, crypto, workloads, dev):
         return ops.Histc(torch.randn(int((1 << 24) * scale) // 4 * 4, generator=g).to(dev), 256, -4.0, 4.0)
 
     rows = []
-    for name in ("im2col_maxpool", "upsample_bnstats", "im2col_histc", "histc_maxpool", "maxpool_bnstats"):
+    names = ("im2col_maxpool", "upsample_bnstats", "im2col_histc", "histc_maxpool", "maxpool_bnstats")
+    scales = (0.25, 0.5, 1.0, 2.0, 4.0)
+    if args.quick:          # a short form for tests: two pairs, three ratios, no crypto rows
+        names, scales = ("upsample_bnstats", "histc_maxpool"), (0.5, 1.0, 2.0)
+    for name in names:
         ka, kb = _lib.DL_PAIRS[name]
-        for scale in (0.25, 0.5, 1.0, 2.0, 4.0):
+        for scale in scales:
             sets = [(mk(ka, 1.0), mk(kb, scale)) for _ in range(NS)]
             ta = graph_region(torch, lambda i: ops.run(sets[i % NS][0]), NS, steps, 3)
             tb = graph_region(torch, lambda i: ops.run(sets[i % NS][1]), NS, steps, 3)
@@ -1152,6 +1276,9 @@ def run_study(args, torch, ops, crypto, workloads, dev):
                          "speedup_horizontal": round(t2 / best_h[0], 3), "speedup_vertical": round(t2 / best_v[0], 3)})
             del sets
             torch.cuda.empty_cache()
+    if args.quick:
+        print(json.dumps({"study": rows}))
+        return
     c3, c4 = workloads.config3(), workloads.config4(dev)
     none = lambda: None
     NE = 1 << 22
@@ -1185,8 +1312,9 @@ def main():
     ap.add_argument("--count", type=int, default=1 << 24, help="nonces per step with --only cfg3|cfg4")
     ap.add_argument("--dag-items", type=int, default=8_388_608)
     ap.add_argument("--no-extras", action="store_true")
-    ap.add_argument("--im2col-path", default="registers", choices=["registers", "bulk"],
-                    help="store path of the im2col role: register tiles + streaming stores, or shared-memory tile + bulk (TMA) stores")
+    ap.add_argument("--im2col-path", default="default", choices=["default", "registers", "bulk"],
+                    help="store path of the im2col role: the compiled choice per kernel / pair, register tiles + "
+                         "streaming stores, or shared-memory tile + bulk (TMA) stores")
     ap.add_argument("--pair-variant", type=int, default=-1,
                     help="force thread-range variant V of the headline pair (tuning aid; default: the compiled-in choice)")
     ap.add_argument("--tune-share", action="store_true",
@@ -1201,6 +1329,7 @@ def main():
                     help="length of the timed region: the K-step pass is repeated until it lasts about this long (at least 50 passes)")
     ap.add_argument("--tune", action="store_true", help="sweep all variants and print the best per kernel / pair")
     ap.add_argument("--tune-skip-crypto", action="store_true", help="with --tune: sweep the DL kernels and pairs only")
+    ap.add_argument("--quick", action="store_true", help="with --study: two pairs and three ratios only")
     ap.add_argument("--study", action="store_true", help="speedup vs ratio of the standalone times, as JSON")
     ap.add_argument("--graph", action="store_true", help="with --only: replay the launches from a CUDA graph")
     args = ap.parse_args()

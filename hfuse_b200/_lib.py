@@ -71,7 +71,7 @@ def exported_symbols() -> list[str]:
     names += ["hfuse_maxpool2d_backward_f32", "hfuse_bn_backward_f32", "hfuse_maxpool_backward_bn_backward_f32"]
     names += ["hfuse_error_string", "hfuse_version", "hfuse_bnstats_workspace_bytes", "hfuse_bnstats_noalloc_f32",
               "hfuse_bnstats_finalize_f64", "hfuse_hits_reset", "hfuse_hash_batch", "hfuse_tune_set",
-              "hfuse_tune_describe", "hfuse_tune_set_share", "hfuse_tune_option", "hfuse_xoshiro256ss_fill", "hfuse_int32_probe", "hfuse_hbm_probe", "hfuse_shard_range"]
+              "hfuse_tune_describe", "hfuse_tune_set_share", "hfuse_tune_option", "hfuse_xoshiro256ss_fill", "hfuse_int32_probe", "hfuse_hbm_probe", "hfuse_hbm_probe_bulk", "hfuse_shard_range"]
     return names
 
 
@@ -156,6 +156,7 @@ def lib() -> C.CDLL:
     L.hfuse_shard_range.restype = _i
     L.hfuse_shard_range.argtypes = [_u64, _i, _i, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
     L.hfuse_hbm_probe.restype, L.hfuse_hbm_probe.argtypes = _i, [_p, _sz, _p, _sz, _p]
+    L.hfuse_hbm_probe_bulk.restype, L.hfuse_hbm_probe_bulk.argtypes = _i, [_p, _sz, _p, _sz, _p]
     L.hfuse_int32_probe.restype, L.hfuse_int32_probe.argtypes = _i, [_i, _u32, _p, C.POINTER(C.c_uint64), _p]
     _lib = L
     return L

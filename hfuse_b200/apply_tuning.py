@@ -38,6 +38,9 @@ def apply(path: str) -> None:
                     continue
                 src, n = re.subn(rf"(kDefault{kind}_{name} = )\d+;", rf"\g<1>{entry['best']};", src)
                 assert n == 1, name
+                if "im2col_bulk" in entry:       # store path of the im2col role in this kernel / pair
+                    src, n = re.subn(rf"(kIm2colBulk_{name} = )\d+;", rf"\g<1>{int(entry['im2col_bulk'])};", src)
+                    assert n == 1, name
         open(p, "w").write(src)
         print("updated", p)
 

@@ -104,6 +104,7 @@ int fill_eth(const void* dag, uint32_t dag_items, const uint8_t* header_hash32, 
     if (reinterpret_cast<uintptr_t>(dag) & 15u) return HFUSE_ERR_ALIGNMENT;
     a.dag = static_cast<const uint4*>(dag);
     a.dag_items = dag_items;
+    a.pow2_mask = (dag_items > 1 && (dag_items & (dag_items - 1)) == 0) ? dag_items - 1 : 0;
     a.mod_magic = ~0ull / dag_items + 1;
     for (int i = 0; i < 4; ++i) a.header[i] = le64(header_hash32 + 8 * i);
     return HFUSE_OK;

@@ -46,14 +46,14 @@ int prep_im2col(HFUSE_IM2COL_PARAMS(), Im2colArgs& a) {
                  ? 1 : 0;
     // tap planes start at multiples of Hc*Wc floats: with Wc % 8 == 0 every row start is 32-byte aligned
     if (a.mode == 1 && ph == 1 && pw == 1 && (Wc % 8) == 0 && (W % 4) == 0 && aligned32(col)) a.mode = 2;
-    a.band = 0; a.bands = 1;
-    if (a.mode >= 1 && ph == 1 && pw == 1 && (W % 4) == 0 && option_get("im2col_store_path") == 1) {
-        // shared-memory tile + bulk stores: as many rows per unit as fit 20 KB per buffer
+    a.band = 0; a.bands = 1; a.bulk_ok = 0;
+    if (a.mode >= 1 && ph == 1 && pw == 1 && (W % 4) == 0) {
+        // shared-memory tile + bulk stores are possible: as many rows per unit as fit 20 KB per buffer
         const long long fit = (20 * 1024) / (12LL * Wc) - 2;
         if (fit >= 1) {
             a.band = (int)(fit < Hc ? fit : Hc);
             a.bands = (int)((Hc + a.band - 1) / a.band);
-            if ((long long)N * C * a.bands <= kMaxItems) a.mode = 3;
+            a.bulk_ok = ((long long)N * C * a.bands <= kMaxItems) ? 1 : 0;
         }
     }
     a.div_bands = make_fastdiv((uint32_t)a.bands);
@@ -167,6 +167,16 @@ int clear_counts(const HistcArgs& a, cudaStream_t s) {
     clear_counts_kernel<<<blocks, 256, 0, s>>>(a.counts, a.nbins);
     return check_launch();
 }
+// Which store path the im2col role takes in the kernel or pair `name`: the option
+// "im2col_store_path" if it was set (0 or 1), else the compiled default of that kernel or pair.
+int default_im2col_bulk(const char* name);
+void choose_path(Im2colArgs& a, const char* name) {
+    if (!a.bulk_ok) return;
+    const int opt = option_get("im2col_store_path", -1);
+    if (opt >= 0 ? opt == 1 : default_im2col_bulk(name) == 1) a.mode = 3;
+}
+template <class A> void choose_path(A&, const char*) {}
+
 // pre_launch returns a negative error, 0, or 1 when the main kernel must be launched as the
 // programmatic dependent of what pre_launch queued
 int pre_launch(const HistcArgs& a, cudaStream_t s) {
@@ -196,6 +206,8 @@ template <class RA, class RB>
 int dispatch_pair(const char* name, int default_variant, typename RA::Args a, typename RB::Args b, cudaStream_t s) {
     const Tune t = tune_get(name);
     const int v = t.variant >= 0 ? t.variant : default_variant;
+    choose_path(a, name);
+    choose_path(b, name);
     const int pa = pre_launch(a, s), pb = pre_launch(b, s);
     if (pa < 0) return pa;
     if (pb < 0) return pb;
@@ -241,6 +253,7 @@ template <class R>
 int dispatch_solo(const char* name, int default_variant, typename R::Args a, cudaStream_t s) {
     const Tune t = tune_get(name);
     const int v = t.variant >= 0 ? t.variant : default_variant;
+    choose_path(a, name);
     const int pa = pre_launch(a, s);
     if (pa < 0) return pa;
     switch (v) {
@@ -278,6 +291,15 @@ int describe_dl_solo(int v, char* buf, size_t n) {
 // default variant per kernel / pair (index into the lists above), chosen by the sweep
 // in bench.py --tune on a B200
 #include "dl_tuned.inc"
+
+int default_im2col_bulk(const char* name) {
+    if (!strcmp(name, "im2col")) return kIm2colBulk_im2col;
+    if (!strcmp(name, "im2col_maxpool")) return kIm2colBulk_im2col_maxpool;
+    if (!strcmp(name, "im2col_bnstats")) return kIm2colBulk_im2col_bnstats;
+    if (!strcmp(name, "im2col_histc")) return kIm2colBulk_im2col_histc;
+    if (!strcmp(name, "im2col_upsample")) return kIm2colBulk_im2col_upsample;
+    return 0;
+}
 
 }  // namespace
 

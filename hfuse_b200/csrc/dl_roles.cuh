@@ -32,6 +32,7 @@ struct Im2colArgs {
                 // 2 = the same with 8 columns per item and 256-bit stores (pad 1, Wc % 8 == 0, col 32-byte aligned),
                 // 3 = 3x3 stride-1 pad-1 through a shared-memory tile and bulk (TMA) stores (run_bulk)
     int band, bands;          // mode 3: output rows per work unit, units per plane
+    int bulk_ok;              // the shape allows mode 3 (the host picks the mode per kernel or pair)
     FastDiv div_bands;        // mode 3: by bands
     FastDiv div_w4, div_hc;   // tile paths: by Wc/4 (mode 1) or Wc/8 (mode 2), and by Hc
     FastDiv div_wc, div_taps, div_kw;   // generic path with fewer than 2^31 outputs (small != 0)
@@ -814,19 +815,25 @@ struct HistcRole {
 // folds them in rank order, so all ranks compute the same bits.  Slots rotate and epochs only
 // grow; a rank can run at most one call ahead of the slowest one (its next kernel cannot end
 // before every rank has delivered), so a slot is never overwritten before it has been read.
-// Slot and epoch of a call come from a call counter kept in the buffer's header ON THE DEVICE:
-// every block reads it when it starts, and the block that finishes last advances it.  The host
-// therefore passes nothing that changes from call to call, so a launch replayed from a CUDA graph
-// moves on to the next slot and epoch like a direct launch does, and a launch that failed on the
-// host leaves the counter where the other ranks' counters are.
+// Slot and epoch of a call come from a call counter kept in the buffer's header ON THE DEVICE.
+// The header holds one 64-bit word: the number of completed exchange launches in its upper half, the
+// number of blocks of the running launch that have checked in in its lower half.  One thread per
+// block adds 1 to it when the block starts: the value it gets back carries the call count (the same
+// for every block of the launch, since the count only moves once all of them have checked in) and
+// the block's ticket.  The block that drew the last ticket moves the word on to the next call
+// (count + 1, tickets back to 0) before it ends.  The add is issued at the start of the block and
+// its result is first needed when the block sends, so it costs no wait.  The host passes nothing
+// that changes from call to call: a launch replayed from a CUDA graph moves on to the next slot
+// and epoch like a direct launch does, and a launch that failed on the host leaves the counter
+// where the other ranks' counters are.
 constexpr int kXchgMaxRanks = 8;
 constexpr int kXchgSlots = 4;
 constexpr int kXchgRowWords = 6;      // 5 used, padded to 48 bytes
 struct XchgLayout {                   // header of an exchange buffer
     unsigned status;                  // set to 1 when a wait ran out of time
-    unsigned calls;                   // exchange launches completed on this buffer
-    unsigned done;                    // blocks of the running launch that have finished their exchange work
-    unsigned pad[61];
+    unsigned pad0;
+    unsigned long long ticket;        // (completed launches << 32) | blocks of the running launch that checked in
+    unsigned pad[60];
     // followed by unsigned long long rows[kXchgSlots][kXchgMaxRanks][C][kXchgRowWords]
 };
 struct BnXchg {
@@ -839,19 +846,19 @@ struct XchgUse {              // which slot a launch writes, and the tag its wor
     unsigned slot;
     unsigned epoch;           // use count of the slot, never 0 (the buffer starts zeroed)
 };
-__device__ __forceinline__ XchgUse xchg_use(const BnXchg& x) {
-    const volatile unsigned* calls = &reinterpret_cast<const XchgLayout*>(x.peer[x.rank])->calls;
-    const unsigned n = *calls;
+// one thread per block, when the block starts; returns the word as it was before this block's ticket
+__device__ __forceinline__ unsigned long long xchg_check_in(const BnXchg& x) {
+    return atomicAdd(&reinterpret_cast<XchgLayout*>(x.peer[x.rank])->ticket, 1ull);
+}
+__device__ __forceinline__ XchgUse xchg_use(unsigned long long word) {
+    const unsigned n = (unsigned)(word >> 32);
     return XchgUse{n % kXchgSlots, n / kXchgSlots + 1u};
 }
-// One thread per block, after the block's last exchange access: the last block to arrive moves
-// the buffer on to the next call and leaves the ticket at zero.
-__device__ __forceinline__ void xchg_block_done(const BnXchg& x, unsigned nblocks) {
-    XchgLayout* h = reinterpret_cast<XchgLayout*>(x.peer[x.rank]);
-    if (atomicAdd(&h->done, 1u) == nblocks - 1u) {
-        h->done = 0u;
-        atomicAdd(&h->calls, 1u);
-    }
+// the same thread, after the block's last exchange access: the block with the last ticket moves
+// the word on to the next call
+__device__ __forceinline__ void xchg_check_out(const BnXchg& x, unsigned long long word, unsigned nblocks) {
+    if ((unsigned)word == nblocks - 1u)
+        atomicAdd(&reinterpret_cast<XchgLayout*>(x.peer[x.rank])->ticket, (1ull << 32) - (unsigned long long)nblocks);
 }
 __device__ __forceinline__ volatile unsigned long long* xchg_row(unsigned char* base, int C, unsigned slot, int src,
                                                                  int c) {
@@ -1037,22 +1044,21 @@ struct BnStatsRole {
     // moments this block sent.  Only the one-slice-per-channel plan defers (the block that owns a
     // unit is then the one that sent it); with slices the exchange already happened in run_impl.
     template <int T>
-    static __device__ __forceinline__ void collect_deferred(const Args& a, const RoleCtx& ctx) {
+    static __device__ __forceinline__ void collect_deferred(const Args& a, const RoleCtx& ctx, unsigned long long word) {
         if (a.S != 1 || (ctx.tid >> 5) != 0) return;
-        const XchgUse use = xchg_use(a.xchg);      // not advanced yet: this block has not reported done
+        const XchgUse use = xchg_use(__shfl_sync(0xffffffffu, word, 0));      // thread 0 holds the block's check-in word
         for (unsigned u = ctx.block; u < (unsigned)a.C; u += ctx.nblocks) xchg_collect(a, use, (int)u, ctx.tid & 31);
     }
 
+    // `word`: the block's check-in word (XCHG only; held by thread 0, see xchg_check_in)
     template <int T, int BAR, bool XCHG, bool DEFER>
-    static __device__ __forceinline__ void run_impl(const Args& a, const RoleCtx& ctx) {
+    static __device__ __forceinline__ void run_impl(const Args& a, const RoleCtx& ctx, unsigned long long word = 0ull) {
         constexpr int NW = T / 32;
         constexpr int UNROLL = 4;
         static_assert(NW <= 32, "one warp folds the per-warp moments");
         float* sh = reinterpret_cast<float*>(ctx.smem);
         const int lane = ctx.tid & 31, warp = ctx.tid >> 5;
         const unsigned units = (unsigned)a.C * (unsigned)a.S;
-        XchgUse use{0u, 0u};
-        if (XCHG) use = xchg_use(a.xchg);
         int parity = 0;
         for (unsigned u = ctx.block; u < units; u += ctx.nblocks, parity ^= 1) {
             const unsigned c = u / a.S, s = u - c * a.S;
@@ -1124,6 +1130,8 @@ struct BnStatsRole {
             if (warp != 0) continue;
             Moments w = (lane < NW) ? Moments{buf[lane], buf[NW + lane], buf[2 * NW + lane]} : Moments{0.f, 0.f, 0.f};
             w = warp_merge(w);
+            XchgUse use{0u, 0u};
+            if (XCHG) use = xchg_use(__shfl_sync(0xffffffffu, word, 0));     // warp 0: thread 0 holds the word
             if (a.S == 1) {
                 complete<XCHG, DEFER>(a, use, (int)c, w, lane);
                 continue;
@@ -1156,18 +1164,24 @@ struct BnStatsRole {
 struct BnStatsXchgRole : BnStatsRole {
     template <int T, int BAR>
     static __device__ __forceinline__ void run(const Args& a, const RoleCtx& ctx) {
-        BnStatsRole::run_impl<T, BAR, true, false>(a, ctx);
-        if (ctx.tid == 0) xchg_block_done(a.xchg, (unsigned)ctx.nblocks);   // warp 0 did this block's exchange
+        unsigned long long word = 0ull;
+        if (ctx.tid == 0) word = xchg_check_in(a.xchg);
+        BnStatsRole::run_impl<T, BAR, true, false>(a, ctx, word);
+        if (ctx.tid == 0) xchg_check_out(a.xchg, word, (unsigned)ctx.nblocks);   // warp 0 did this block's exchange
     }
-    // the two halves for a kernel that puts other work between sending and collecting
+    // The two halves for a kernel that puts other work between sending and collecting; run_early
+    // returns the block's check-in word (in thread 0), which run_late takes back.
     template <int T, int BAR>
-    static __device__ __forceinline__ void run_early(const Args& a, const RoleCtx& ctx) {
-        BnStatsRole::run_impl<T, BAR, true, true>(a, ctx);
+    static __device__ __forceinline__ unsigned long long run_early(const Args& a, const RoleCtx& ctx) {
+        unsigned long long word = 0ull;
+        if (ctx.tid == 0) word = xchg_check_in(a.xchg);
+        BnStatsRole::run_impl<T, BAR, true, true>(a, ctx, word);
+        return word;
     }
     template <int T, int BAR>
-    static __device__ __forceinline__ void run_late(const Args& a, const RoleCtx& ctx) {
-        BnStatsRole::collect_deferred<T>(a, ctx);
-        if (ctx.tid == 0) xchg_block_done(a.xchg, (unsigned)ctx.nblocks);
+    static __device__ __forceinline__ void run_late(const Args& a, const RoleCtx& ctx, unsigned long long word) {
+        BnStatsRole::collect_deferred<T>(a, ctx, word);
+        if (ctx.tid == 0) xchg_check_out(a.xchg, word, (unsigned)ctx.nblocks);
     }
 };
 

@@ -54,9 +54,9 @@ fused_share_kernel(const __grid_constant__ typename RoleA::Args a, const __grid_
         RoleA::template run_range<TA>(a, ctx, 0u, split);
     } else {
         RoleCtx ctx{tid - TA, (int)blockIdx.x, (int)gridDim.x, smem + smem_off_b};
-        RoleB::template run_early<TB, 2>(b, ctx);
+        const auto token = RoleB::template run_early<TB, 2>(b, ctx);
         RoleA::template run_range<TB>(a, ctx, split, items);
-        RoleB::template run_late<TB, 2>(b, ctx);
+        RoleB::template run_late<TB, 2>(b, ctx, token);
     }
 }
 

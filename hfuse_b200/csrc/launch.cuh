@@ -78,16 +78,17 @@ inline Tune tune_get(const char* name) {
 }
 
 // ---- options: named integer switches between alternative code paths -----------------------
-// "im2col_store_path": 0 = register tiles and streaming stores (default), 1 = shared-memory tile
-// and bulk (TMA) stores where the shape allows it.
+// "im2col_store_path": -1 (unset) = the compiled choice of each kernel and pair, 0 = register tiles
+// and streaming stores everywhere, 1 = shared-memory tile and bulk (TMA) stores wherever the shape
+// allows it.
 inline std::map<std::string, int>& option_table() {
     static std::map<std::string, int> t;
     return t;
 }
-inline int option_get(const char* name) {
+inline int option_get(const char* name, int unset) {
     std::lock_guard<std::mutex> lk(tune_mutex());
     auto it = option_table().find(name);
-    return it == option_table().end() ? 0 : it->second;
+    return it == option_table().end() ? unset : it->second;
 }
 
 // more than 48 KB of dynamic shared memory has to be asked for once per kernel and device

@@ -353,12 +353,12 @@ HFUSE_API int hfuse_tune_describe(const char* pair, int variant, char* buf, size
  * waiting for theirs.  Any other name: HFUSE_ERR_UNKNOWN_PAIR. */
 HFUSE_API int hfuse_tune_set_share(const char* pair, int permille);
 
-/* Named switches between alternative code paths of a kernel (default 0).  Unknown name:
- * HFUSE_ERR_UNKNOWN_PAIR.
- *   "im2col_store_path": 0 = the im2col role keeps its patch in registers and writes the taps with
- *       256-bit streaming stores; 1 = 3x3 / stride 1 / pad 1 shapes go through a shared-memory
- *       tile and leave as bulk (TMA) copies of whole tap bands.  Same bytes either way; kept as
- *       a measured alternative (the streaming stores are the faster of the two on B200). */
+/* Named switches between alternative code paths of a kernel.  Unknown name: HFUSE_ERR_UNKNOWN_PAIR.
+ *   "im2col_store_path": how the im2col role writes 3x3 / stride 1 / pad 1 shapes.  0 = it keeps
+ *       its patch in registers and writes the taps with 256-bit streaming stores; 1 = it goes
+ *       through a shared-memory tile and the taps leave as bulk (TMA) copies of whole bands of
+ *       rows; -1 (the default) = whichever the sweep on B200 found faster for the kernel or pair
+ *       that is called.  Same bytes either way. */
 HFUSE_API int hfuse_tune_option(const char* name, int value);
 
 /* Host utility (no counterpart in the reference, which is single-GPU): the share of `total` batch
@@ -384,6 +384,9 @@ HFUSE_API int hfuse_int32_probe(int mix, uint32_t iters, uint32_t* sink, uint64_
  * the memory-traffic mix of a kernel, without the kernel.  read_bytes / 16 <= write_bytes / 32;
  * dst 32-byte aligned, src 16-byte aligned, sizes multiples of 32 and 16. */
 HFUSE_API int hfuse_hbm_probe(const void* src, size_t read_bytes, void* dst, size_t write_bytes, hfuse_stream_t stream);
+/* The same traffic with the writes issued as bulk (TMA) copies of 8 KB from shared memory instead of
+ * streaming stores: write_bytes a multiple of 8192, read_bytes <= write_bytes. */
+HFUSE_API int hfuse_hbm_probe_bulk(const void* src, size_t read_bytes, void* dst, size_t write_bytes, hfuse_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -91,6 +91,7 @@ def test_fused_search_needs_two_different_hit_records_and_a_count_that_fits_the_
     assert L.hfuse_tune_option(b"im2col_store_path", 2) == -1
     assert L.hfuse_tune_option(b"nothing", 1) == -7
     assert L.hfuse_tune_option(b"im2col_store_path", 0) == 0
+    assert L.hfuse_tune_option(b"im2col_store_path", -1) == 0        # back to the compiled choice per kernel / pair
 
 
 def test_ops_refuse_cpu_tensors():

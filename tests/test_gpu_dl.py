@@ -236,16 +236,17 @@ def test_im2col_through_shared_memory_and_bulk_stores_gives_the_same_bytes(dev):
              ((2, 2, 10, 8), (3, 3, 2, 2, 1, 1, 1, 1)),      # pad 2: usual path
              ((1, 2, 9, 11), (5, 2, 2, 1, 2, 3, 1, 2))]      # generic path
     try:
-        _lib.tune_option("im2col_store_path", 1)
-        for shape, prm in cases:
-            x = torch.rand(*shape, generator=g) * 2 - 1
-            kh, kw, ph, pw, sh, sw, dh, dw = prm
-            want = dl.im2col_torch(x, *prm)
-            for v in range(len(_lib.tune_variants("im2col"))):
-                _lib.tune_set("im2col", v, 0)
-                out = ops.im2col(x.to(dev), (kh, kw), (ph, pw), (sh, sw), (dh, dw))
-                assert torch.equal(out.cpu(), want), (shape, prm, v)
-            _lib.tune_set("im2col", -1, 0)
+        for path in (0, 1):                                  # both paths, whatever the compiled choice is
+            _lib.tune_option("im2col_store_path", path)
+            for shape, prm in cases:
+                x = torch.rand(*shape, generator=g) * 2 - 1
+                kh, kw, ph, pw, sh, sw, dh, dw = prm
+                want = dl.im2col_torch(x, *prm)
+                for v in range(len(_lib.tune_variants("im2col"))):
+                    _lib.tune_set("im2col", v, 0)
+                    out = ops.im2col(x.to(dev), (kh, kw), (ph, pw), (sh, sw), (dh, dw))
+                    assert torch.equal(out.cpu(), want), (path, shape, prm, v)
+                _lib.tune_set("im2col", -1, 0)
         # the benchmark shape, alone and fused with max-pool (another role beside it in the block)
         w = workloads.config0(batch=4)
         a = ops.Im2col(w["im"].to(dev), **w["im2col"])
@@ -263,7 +264,7 @@ def test_im2col_through_shared_memory_and_bulk_stores_gives_the_same_bytes(dev):
         ops.run_pair(a, h)
         assert torch.equal(a.out.cpu(), want)
     finally:
-        _lib.tune_option("im2col_store_path", 0)
+        _lib.tune_option("im2col_store_path", -1)
         _lib.tune_set("im2col", -1, 0)
     with pytest.raises(_lib.HfuseError):
         _lib.tune_option("no_such_option", 1)

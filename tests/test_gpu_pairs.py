@@ -44,25 +44,29 @@ def test_fused_equals_standalone_for_every_variant(dev, pair):
     ops.run(b)
     ra, rb = _snapshot(a), _snapshot(b)
     try:
-        for v in range(len(_lib.tune_variants(pair))):
-            _lib.tune_set(pair, v, 0)
-            for t in a.result() if isinstance(a.result(), tuple) else (a.result(),):
-                t.fill_(0) if t.dtype != torch.int64 else t.fill_(-1)
-            for t in b.result() if isinstance(b.result(), tuple) else (b.result(),):
-                t.fill_(0) if t.dtype != torch.int64 else t.fill_(-1)
-            ops.run_pair(a, b)
-            if ka == "bnstats" or kb == "bnstats":
-                # the statistics role splits channels into slices by grid size, so its rounding may
-                # differ between launch shapes: compare within the specified tolerance instead
-                bn_res, bn_ref = (_snapshot(a), ra) if ka == "bnstats" else (_snapshot(b), rb)
-                for x, y in zip(bn_res, bn_ref):
-                    np.testing.assert_allclose(x.cpu().numpy(), y.cpu().numpy(), rtol=2e-6)
-                other_res, other_ref = (_snapshot(b), rb) if ka == "bnstats" else (_snapshot(a), ra)
-                assert _same(other_res, other_ref), (pair, v)
-            else:
-                assert _same(_snapshot(a), ra) and _same(_snapshot(b), rb), (pair, v)
+        for path in ((0, 1) if "im2col" in pair else (None,)):      # both store paths of the im2col role
+            if path is not None:
+                _lib.tune_option("im2col_store_path", path)
+            for v in range(len(_lib.tune_variants(pair))):
+                _lib.tune_set(pair, v, 0)
+                for t in a.result() if isinstance(a.result(), tuple) else (a.result(),):
+                    t.fill_(0) if t.dtype != torch.int64 else t.fill_(-1)
+                for t in b.result() if isinstance(b.result(), tuple) else (b.result(),):
+                    t.fill_(0) if t.dtype != torch.int64 else t.fill_(-1)
+                ops.run_pair(a, b)
+                if ka == "bnstats" or kb == "bnstats":
+                    # the statistics role splits channels into slices by grid size, so its rounding may
+                    # differ between launch shapes: compare within the specified tolerance instead
+                    bn_res, bn_ref = (_snapshot(a), ra) if ka == "bnstats" else (_snapshot(b), rb)
+                    for x, y in zip(bn_res, bn_ref):
+                        np.testing.assert_allclose(x.cpu().numpy(), y.cpu().numpy(), rtol=2e-6)
+                    other_res, other_ref = (_snapshot(b), rb) if ka == "bnstats" else (_snapshot(a), ra)
+                    assert _same(other_res, other_ref), (pair, path, v)
+                else:
+                    assert _same(_snapshot(a), ra) and _same(_snapshot(b), rb), (pair, path, v)
     finally:
         _lib.tune_set(pair, -1, 0)
+        _lib.tune_option("im2col_store_path", -1)
 
 
 def test_pair_config0_against_oracle(dev):
