@@ -47,8 +47,8 @@ struct Im2colRole {
 
     // 3x3 / stride 1 / pad 1 / dilation 1 (so Wc == W, Hc == H), W % 4 == 0, through shared memory.
     // Work unit = (plane, band of `band` output rows).  The role loads the band's band + 2 input
-    // rows once (16-byte loads) and lays them down three times in shared memory, shifted by one
-    // column to the right, not at all, and one to the left, with the zero padding written in:
+    // rows once (16-byte loads) and lays them down three times in shared memory (16-byte stores),
+    // shifted by one column to the right, not at all, and one to the left, with the zero padding written in:
     // copy j, row r, column w holds im[h0 - 1 + r][w - 1 + j].  Tap (i, j) of the band is then the
     // CONTIGUOUS block of rows i .. i + band - 1 of copy j, and its place in `col` is contiguous
     // too (rows h0 .. h0 + band - 1 of one tap plane), so each of the nine taps leaves as one bulk
@@ -72,21 +72,30 @@ struct Im2colRole {
             if (ctx.tid == 0) bulk_wait_read<1>();
             role_sync<BAR, T>();
             const float* src = a.im + (size_t)plane * a.H * a.W;
-            for (int it = ctx.tid; it < (nrows + 2) * W4; it += T) {
-                const int r = it / W4, m = it - r * W4;
+            // One 16-byte load per item (row r, columns 4m .. 4m+3); the columns just outside come
+            // from the neighbouring lanes (a warp walks along the rows), so each of the three copies
+            // is written with one aligned 16-byte shared-memory store.  Warp-uniform trip count:
+            // every lane takes part in the shuffles.
+            const int total = (nrows + 2) * W4;
+            const int lane = ctx.tid & 31;
+            for (int base = ctx.tid & ~31; base < total; base += T) {
+                const int it = base + lane;
+                const bool live = it < total;
+                const int r = live ? it / W4 : 0, m = live ? it - r * W4 : 0;
                 const int hi = h0 - 1 + r;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (hi >= 0 && hi < a.H) v = __ldg(reinterpret_cast<const float4*>(src + (size_t)hi * a.W + 4 * m));
+                const bool row_ok = live && hi >= 0 && hi < a.H;
+                const float* p = src + (size_t)(row_ok ? hi : 0) * a.W + 4 * m;
+                const float4 v = row_ok ? __ldg(reinterpret_cast<const float4*>(p)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                float left = __shfl_up_sync(0xffffffffu, v.w, 1), right = __shfl_down_sync(0xffffffffu, v.x, 1);
+                if (lane == 0 && m > 0) left = row_ok ? __ldg(p - 1) : 0.f;            // the neighbour sits in another warp
+                if (lane == 31 && m + 1 < W4) right = row_ok ? __ldg(p + 4) : 0.f;
+                if (m == 0) left = 0.f;                                                 // zero padding at the row ends
+                if (m + 1 == W4) right = 0.f;
+                if (!live) continue;
                 float* row = tile + r * Wc + 4 * m;
-                *reinterpret_cast<float4*>(row + copy_elems) = v;                 // j = 1: in place
-                float* c0 = row + 1;                                              // j = 0: one column to the right
-                c0[0] = v.x; c0[1] = v.y; c0[2] = v.z;
-                if (m + 1 < W4) c0[3] = v.w;
-                if (m == 0) row[0] = 0.f;                                         // left padding
-                float* c2 = row + 2 * copy_elems - 1;                             // j = 2: one column to the left
-                if (m > 0) c2[0] = v.x;
-                c2[1] = v.y; c2[2] = v.z; c2[3] = v.w;
-                if (m + 1 == W4) c2[4] = 0.f;                                     // right padding
+                *reinterpret_cast<float4*>(row) = make_float4(left, v.x, v.y, v.z);                      // j = 0: im[w - 1]
+                *reinterpret_cast<float4*>(row + copy_elems) = v;                                        // j = 1
+                *reinterpret_cast<float4*>(row + 2 * copy_elems) = make_float4(v.y, v.z, v.w, right);    // j = 2: im[w + 1]
             }
             fence_proxy_async_shared();
             role_sync<BAR, T>();

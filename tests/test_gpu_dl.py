@@ -325,3 +325,12 @@ def test_hbm_probe_copies_what_it_reads_and_rejects_bad_arguments(dev):
     assert L.hfuse_hbm_probe(src.data_ptr(), 16, dst.data_ptr(), 0, None) == -1
     assert L.hfuse_hbm_probe(src.data_ptr(), 64, dst.data_ptr(), 64, None) == -1              # more loads than stores
     assert L.hfuse_hbm_probe(src.data_ptr(), 16, dst.data_ptr() + 16, 32, None) == -2         # alignment
+    # the bulk-store form: 8 KB chunks, the read part of every chunk first, the rest the same constant
+    out = torch.zeros(3 * 2048, device=dev)                      # three chunks of 2048 floats
+    inp = torch.randn(4 * 600, device=dev)                       # 600 16-byte loads: 200 per chunk
+    assert L.hfuse_hbm_probe_bulk(inp.data_ptr(), inp.numel() * 4, out.data_ptr(), out.numel() * 4, None) == 0
+    got, want = out.cpu().view(3, 512, 4), inp.cpu().view(3, 200, 4)
+    assert torch.equal(got[:, :200], want)
+    assert torch.equal(got[:, 200:], torch.tensor([1., 2., 3., 4.]).expand(3, 312, 4))
+    assert L.hfuse_hbm_probe_bulk(None, 0, out.data_ptr(), out.numel() * 4, None) == 0        # write only
+    assert L.hfuse_hbm_probe_bulk(None, 0, out.data_ptr(), 4096, None) == -1                  # not whole chunks
