@@ -23,13 +23,13 @@ from . import _lib
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
 
 
-def apply(path: str) -> None:
+def apply(path: str, csrc: str = CSRC) -> None:
     with open(path) as f:
         text = f.read()
     res = json.loads(text[text.index("{"):])
     for inc, solos, pairs in (("dl_tuned.inc", _lib.DL_SOLO, _lib.DL_PAIRS),
                               ("crypto_tuned.inc", _lib.CRYPTO_SOLO, _lib.CRYPTO_PAIRS)):
-        p = os.path.join(CSRC, inc)
+        p = os.path.join(csrc, inc)
         src = open(p).read()
         for kind, names in (("Solo", solos), ("Pair", pairs)):
             for name in names:
@@ -45,14 +45,14 @@ def apply(path: str) -> None:
         print("updated", p)
 
 
-def apply_share(path: str) -> None:
+def apply_share(path: str, csrc: str = CSRC) -> None:
     """Result of `torchrun ... bench.py --gpus N --tune-share`: the thread split and the upsample share
     of the exchange pair, for two ranks (N <= 2) or for more (the `_wide` defaults)."""
     with open(path) as f:
         text = f.read()
     res = json.loads(text[text.index("{"):])
     suffix = "_wide" if int(res["n_gpus"]) > 2 else ""
-    p = os.path.join(CSRC, "dl_tuned.inc")
+    p = os.path.join(csrc, "dl_tuned.inc")
     src = open(p).read()
     for key, val in ((f"kDefaultPair_upsample_bnstats_allreduce{suffix}", res["best"]["index"]),
                      (f"kDefaultShare_upsample_bnstats_allreduce{suffix}", res["best"]["share_permille"])):
