@@ -18,8 +18,8 @@ Timing: the K steps of one pass are replayed from a CUDA graph; the timed region
 such passes (R chosen so that the region lasts about a second, at least 50), every pass
 bracketed by CUDA events on the launching stream (for small K several passes share one
 graph, with event-record nodes between them), barrier + synchronize on both sides of
-the region, every pass's time the max over ranks, the median pass reported (min, max and
-mean beside it).  The steps rotate over several independent buffer sets whose combined
+the region; every rank takes the median of its passes and the maximum over ranks is
+reported (mean, min and max beside it).  The steps rotate over several independent buffer sets whose combined
 footprint is several times the L2, so no step finds its inputs in cache.  After the timed
 region the results left in the buffers are compared with the oracle (`parity_ok`).
 
@@ -660,12 +660,19 @@ def run_ours(args):
     torch.cuda.synchronize()
     barrier()
     clocks = sampler.stop()
-    passes = torch.tensor(pass_ms, dtype=torch.float64, device=dev)
+    # Every rank has the times of its own R passes.  Coupled ranks run at one common rate but a rank
+    # that got ahead in one pass waits in the next, so its passes alternate around that rate: the
+    # figure reported is each rank's MEDIAN pass, the maximum of those over the ranks (taking the
+    # maximum pass by pass first would count every such alternation as a slow pass).  Beside it:
+    # the mean (each rank's whole region, maximum over ranks) and the extreme passes of any rank.
+    mine = torch.tensor(pass_ms, dtype=torch.float64, device=dev)
+    stats = torch.stack([mine.median(), mine.mean(), mine.max(), -mine.min()])
     if use_dist:
         import torch.distributed as dist
-        dist.all_reduce(passes, op=dist.ReduceOp.MAX)
-    passes = passes.cpu()
-    ms = float(passes.median())                    # one pass of K steps
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    stats = stats.cpu()
+    ms = float(stats[0])                           # one pass of K steps
+    ms_mean, ms_max, ms_min = float(stats[1]), float(stats[2]), -float(stats[3])
     launches = per_step_launches * K * R
     t_step = ms / K                                # ms per step = per launch of the fused kernel
 
@@ -788,13 +795,13 @@ def run_ours(args):
         "config": {"workload": WORKLOAD, "l2": f"steps rotate over {NSETS} independent buffer sets "
                                f"({NSETS * nbytes >> 20} MiB in total, L2 is 126 MB)",
                    "launch": launch_mode,
-                   "timed": {"passes": R, "steps_per_pass": K, "region_ms": round(float(passes.sum()), 2),
+                   "timed": {"passes": R, "steps_per_pass": K, "region_ms": round(ms_mean * R, 2),
                              "us_per_step_median": round(t_step * 1e3, 3),
-                             "us_per_step_min": round(float(passes.min()) / K * 1e3, 3),
-                             "us_per_step_max": round(float(passes.max()) / K * 1e3, 3),
-                             "us_per_step_mean": round(float(passes.mean()) / K * 1e3, 3),
-                             "rule": "every pass = K steps between two CUDA events on the launching stream, "
-                                     "max over ranks per pass, median over passes"},
+                             "us_per_step_min": round(ms_min / K * 1e3, 3),
+                             "us_per_step_max": round(ms_max / K * 1e3, 3),
+                             "us_per_step_mean": round(ms_mean / K * 1e3, 3),
+                             "rule": "every pass = K steps between two CUDA events on the launching stream; "
+                                     "per rank the median pass (and the mean of its region), max over ranks"},
                    "parallelism": f"batch-sharded x{world} (every rank its own draw of the per-GPU batch)",
                    "collective": collective, "host_binding": binding},
         "gpu_launches": launches,
@@ -932,14 +939,18 @@ def run_tune_share(args, torch, _lib, ex, sets, nsets, dev, rank, barrier, use_d
     name = "upsample_bnstats_allreduce"
     descr = _lib.tune_variants(name)
     variants = [v for v, d in enumerate(descr) if ":0:" not in d]
-    shares = (0, 100, 200, 300, 400, 500)
+    shares = (0, 100, 200, 300, 400, 500, "pool")       # "pool": items drawn from a cursor by both ranges
     reps, gsteps = 6, 4 * nsets
     table = {}
     for v in variants:
         row = {}
         for share in shares:
             _lib.tune_set(name, v, 0)
-            _lib.tune_set_share(name, share)
+            if share == "pool":
+                _lib.tune_set_share(name, -1)
+                _lib.tune_option("exchange_pair_pool", 1)
+            else:
+                _lib.tune_set_share(name, share)
             for i in range(nsets):
                 ex.run_pair(*sets[i])
             torch.cuda.synchronize()
@@ -963,13 +974,16 @@ def run_tune_share(args, torch, _lib, ex, sets, nsets, dev, rank, barrier, use_d
             row[str(share)] = round(float(t.item()) / (reps * gsteps) * 1e3, 2)
             del graph
         table[descr[v]] = row
+    _lib.tune_option("exchange_pair_pool", -1)
     _lib.tune_set(name, -1, 0)
     _lib.tune_set_share(name, -1)
     timed_out = ex.timed_out()
     if rank == 0:
         best = min(((t, d, sh) for d, row in table.items() for sh, t in row.items()))
         print(json.dumps({"pair": name, "n_gpus": args.gpus, "unit": "us per step, max over ranks",
-                          "best": {"variant": best[1], "index": descr.index(best[1]), "share_permille": int(best[2]), "us": best[0]},
+                          "best": {"variant": best[1], "index": descr.index(best[1]),
+                                   "share_permille": -1 if best[2] == "pool" else int(best[2]),
+                                   "pool": best[2] == "pool", "us": best[0]},
                           "exchange_timed_out": timed_out, "table": table}))
     if use_dist:
         shutdown(torch, None)

@@ -54,8 +54,13 @@ def apply_share(path: str, csrc: str = CSRC) -> None:
     suffix = "_wide" if int(res["n_gpus"]) > 2 else ""
     p = os.path.join(csrc, "dl_tuned.inc")
     src = open(p).read()
-    for key, val in ((f"kDefaultPair_upsample_bnstats_allreduce{suffix}", res["best"]["index"]),
-                     (f"kDefaultShare_upsample_bnstats_allreduce{suffix}", res["best"]["share_permille"])):
+    if res["best"].get("pool"):       # the cursor form won: one thread split for any number of ranks
+        pairs = (("kDefaultPool_upsample_bnstats_allreduce", 1),
+                 ("kDefaultPoolPair_upsample_bnstats_allreduce", res["best"]["index"]))
+    else:
+        pairs = ((f"kDefaultPair_upsample_bnstats_allreduce{suffix}", res["best"]["index"]),
+                 (f"kDefaultShare_upsample_bnstats_allreduce{suffix}", res["best"]["share_permille"]))
+    for key, val in pairs:
         src, n = re.subn(rf"({key} = )\d+;", rf"\g<1>{int(val)};", src)
         assert n == 1, key
     open(p, "w").write(src)

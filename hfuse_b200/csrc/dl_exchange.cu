@@ -151,9 +151,18 @@ int hfuse_upsample_bnstats_allreduce_f32(HFUSE_UPSAMPLE_PARAMS(a_), HFUSE_BNSTAT
     if (int rc = prep_upsample(UPSAMPLE_NAMES(a_), a)) return rc;
     if (int rc = prep_bnstats(BNSTATS_NAMES(b_), b)) return rc;
     if (int rc = describe_exchange(ex, b_C, b.xchg)) return rc;
-    // Its own tuning entry.  The statistics range sends its moments, then works through a share of
-    // the upsample and only then waits for the peers, so the best split gives that range more
-    // threads than the single-GPU pair does (it should finish its own work early).
+    // Its own tuning entry.  By default the upsample's items are drawn from a cursor by the warps of
+    // both thread ranges (the statistics range joins once it has sent its moments; its first warp
+    // collects the peers' before it joins), so the statistics range can be large, send early, and
+    // still leave nobody idle.  The older form (a fixed share of the upsample handed to the
+    // statistics range, hfuse_tune_set_share) runs when a share has been set or the option
+    // "exchange_pair_pool" is 0.
+    const Tune t = tune_get("upsample_bnstats_allreduce");
+    const int opt = option_get("exchange_pair_pool", -1);
+    const bool pool = t.share_permille < 0 && (opt >= 0 ? opt == 1 : kDefaultPool_upsample_bnstats_allreduce == 1);
+    if (pool)
+        return dispatch_pair_pool<UpsampleRole, BnStatsXchgRole>("upsample_bnstats_allreduce",
+                                                                 kDefaultPoolPair_upsample_bnstats_allreduce, a, b, S_(stream));
     const bool wide = ex->world > 2;      // measured at 2 and at 8 ranks (bench.py --tune-share)
     return dispatch_pair_share<UpsampleRole, BnStatsXchgRole>(
         "upsample_bnstats_allreduce",

@@ -249,6 +249,28 @@ int dispatch_pair_share(const char* name, int default_variant, int default_share
     return HFUSE_ERR_BAD_ARG;
 }
 
+// pairs whose first role's items are drawn from a cursor by both thread ranges (launch_pair_pool)
+template <class RA, class RB>
+int dispatch_pair_pool(const char* name, int default_variant, typename RA::Args a, typename RB::Args b, cudaStream_t s) {
+    const Tune t = tune_get(name);
+    const int v = t.variant >= 0 ? t.variant : default_variant;
+    const int pa = pre_launch(a, s), pb = pre_launch(b, s);
+    if (pa < 0) return pa;
+    if (pb < 0) return pb;
+    const bool dep = pa > 0 || pb > 0;
+    switch (v) {
+#define X(I, TA, TB, MB) \
+    case I: return launch_pair_pool<RA, RB, TA, TB, MB>(a, b, t.blocks_per_sm, s, dep);
+        DL_PAIR_VARIANTS(X)
+#undef X
+#define X(I, T, MB) \
+    case I: return launch_vpair<RA, RB, T, MB>(a, b, t.blocks_per_sm, s, dep);
+        DL_VPAIR_VARIANTS(X)
+#undef X
+    }
+    return HFUSE_ERR_BAD_ARG;
+}
+
 template <class R>
 int dispatch_solo(const char* name, int default_variant, typename R::Args a, cudaStream_t s) {
     const Tune t = tune_get(name);

@@ -60,6 +60,41 @@ fused_share_kernel(const __grid_constant__ typename RoleA::Args a, const __grid_
     }
 }
 
+// The same pair with the split of role A's items decided while the kernel runs: every warp of
+// the block, whichever range it belongs to, draws 32-item chunks of role A's work from one cursor
+// in shared memory.  Role A's range draws from the start; role B's range runs the first half of
+// its own work (compute and send) and then joins the draw, except for its first warp, which
+// first runs the second half (collect) and joins when the peers' answers are in.  Role B's range
+// can therefore be given many threads (it sends early) without leaving those threads idle
+// afterwards, and the wait for the peers is off the kernel's critical path, whatever the number of
+// ranks.  A role A whose shape has no chunked path keeps
+// all of its work in its own range.
+template <class RoleA, class RoleB, int TA, int TB, int MINB>
+__global__ void __launch_bounds__(TA + TB, MINB)
+fused_pool_kernel(const __grid_constant__ typename RoleA::Args a, const __grid_constant__ typename RoleB::Args b,
+                  int smem_off_b) {
+    static_assert(TA % 32 == 0 && TB % 32 == 0, "ranges are whole warps, so the guard never splits a warp");
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ unsigned pool_cursor;
+    const int tid = (int)threadIdx.x;
+    if (tid == 0) pool_cursor = 0u;
+    __syncthreads();          // the only use of barrier 0: before either role has started
+    const bool pooled = RoleA::splittable(a);
+    if (tid < TA) {
+        RoleCtx ctx{tid, (int)blockIdx.x, (int)gridDim.x, smem};
+        if (pooled) RoleA::run_pool(a, ctx.block, ctx.nblocks, &pool_cursor, (unsigned)tid & 31u);
+        else RoleA::template run<TA, 1>(a, ctx);
+    } else {
+        RoleCtx ctx{tid - TA, (int)blockIdx.x, (int)gridDim.x, smem + smem_off_b};
+        const auto token = RoleB::template run_early<TB, 2>(b, ctx);
+        // The second half is the business of the range's first warp only: it waits for the peers
+        // while the range's other warps are already drawing chunks, and joins them afterwards, so
+        // the wait is neither at the end of the kernel nor in anybody's way.
+        RoleB::template run_late<TB, 2>(b, ctx, token);
+        if (pooled) RoleA::run_pool(a, ctx.block, ctx.nblocks, &pool_cursor, (unsigned)tid & 31u);
+    }
+}
+
 // Vertical fusion, the reference's `vfuse` presets (tools/llvm-smart-fuser/main.cpp:182-193,
 // include/KernelFusion.h:75-78): every thread range starts at 0, i.e. the SAME threads run
 // body 1 and then body 2, block = max(T1, T2).  Kept as the third column of the comparison

@@ -81,6 +81,9 @@ inline Tune tune_get(const char* name) {
 // "im2col_store_path": -1 (unset) = the compiled choice of each kernel and pair, 0 = register tiles
 // and streaming stores everywhere, 1 = shared-memory tile and bulk (TMA) stores wherever the shape
 // allows it.
+// "exchange_pair_pool": -1 (unset) = the compiled choice, 1 = the exchange pair draws the upsample's
+// items from a cursor shared by both thread ranges (fused_pool_kernel), 0 = it hands a fixed share
+// of them to the statistics range (fused_share_kernel, hfuse_tune_set_share).
 inline std::map<std::string, int>& option_table() {
     static std::map<std::string, int> t;
     return t;
@@ -192,6 +195,23 @@ int launch_pair_share(typename RA::Args a, typename RB::Args b, int blocks_per_s
         split = items - (unsigned)(given / row * row);
     }
     return launch_kernel(kern, grid, TA + TB, smem, s, dependent, a, b, smem_a, split, items);
+}
+
+// ---- two roles side by side, role A's items drawn from a cursor by the warps of both ranges -----
+template <class RA, class RB, int TA, int TB, int MINB>
+int launch_pair_pool(typename RA::Args a, typename RB::Args b, int blocks_per_sm, cudaStream_t s, bool dependent = false) {
+    DeviceFacts f;
+    if (int rc = device_facts(f)) return rc;
+    auto kern = fused_pool_kernel<RA, RB, TA, TB, MINB>;
+    if (int rc = RA::plan(a, TA, f.sms * MINB)) return rc;
+    if (int rc = RB::plan(b, TB, f.sms * MINB)) return rc;
+    const int smem_a = (RA::smem_bytes(a, TA) + 15) & ~15;
+    const size_t smem = (size_t)smem_a + (size_t)RB::smem_bytes(b, TB);
+    const int bps = blocks_per_sm > 0 ? blocks_per_sm : resident_blocks((const void*)kern, TA + TB, smem);
+    const int grid = f.sms * bps;
+    if (int rc = RA::plan(a, TA, grid)) return rc;
+    if (int rc = RB::plan(b, TB, grid)) return rc;
+    return launch_kernel(kern, grid, TA + TB, smem, s, dependent, a, b, smem_a);
 }
 
 // ---- the same threads run both roles one after the other (vertical fusion) ------------------

@@ -358,7 +358,12 @@ HFUSE_API int hfuse_tune_set_share(const char* pair, int permille);
  *       its patch in registers and writes the taps with 256-bit streaming stores; 1 = it goes
  *       through a shared-memory tile and the taps leave as bulk (TMA) copies of whole bands of
  *       rows; -1 (the default) = whichever the sweep on B200 found faster for the kernel or pair
- *       that is called.  Same bytes either way. */
+ *       that is called.  Same bytes either way.
+ *   "exchange_pair_pool": how hfuse_upsample_bnstats_allreduce_f32 divides the upsample between its
+ *       two thread ranges.  1 = every warp of the block draws 32-item chunks from one cursor (the
+ *       statistics range joins after it has sent its moments); 0 = a fixed share goes to the
+ *       statistics range (hfuse_tune_set_share; setting a share selects this form too); -1 (the
+ *       default) = the compiled choice. */
 HFUSE_API int hfuse_tune_option(const char* name, int value);
 
 /* Host utility (no counterpart in the reference, which is single-GPU): the share of `total` batch

@@ -92,6 +92,8 @@ def test_fused_search_needs_two_different_hit_records_and_a_count_that_fits_the_
     assert L.hfuse_tune_option(b"nothing", 1) == -7
     assert L.hfuse_tune_option(b"im2col_store_path", 0) == 0
     assert L.hfuse_tune_option(b"im2col_store_path", -1) == 0        # back to the compiled choice per kernel / pair
+    assert L.hfuse_tune_option(b"exchange_pair_pool", 1) == 0
+    assert L.hfuse_tune_option(b"exchange_pair_pool", -1) == 0
 
 
 def test_ops_refuse_cpu_tensors():

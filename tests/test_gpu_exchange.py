@@ -74,6 +74,26 @@ def test_statistics_range_takes_over_any_share_of_the_upsample(dev):
         _lib.tune_set("upsample_bnstats_allreduce", -1, 0)
         _lib.tune_set_share("upsample_bnstats_allreduce", -1)
         ex.close()
+    # the cursor form: every warp of either range draws chunks of the upsample; same bits for every split
+    ex = BnExchange(40)
+    try:
+        _lib.tune_option("exchange_pair_pool", 1)
+        for variant in range(len(_lib.tune_variants("upsample_bnstats_allreduce"))):
+            _lib.tune_set("upsample_bnstats_allreduce", variant, 0)
+            for shape, kw in cases:
+                up = torch.rand(*shape, generator=g)
+                a, b = ops.Upsample(up.to(dev), **kw), ops.BnStats(x.to(dev), 1e-5)
+                a.out.fill_(float("nan"))
+                ex.run_pair(a, b)
+                oh, ow = a.out.shape[-2:]
+                assert np.array_equal(a.out.cpu().numpy(), dl.upsample_numpy(up.numpy(), oh, ow)), (variant, shape)
+                np.testing.assert_allclose(b.mean.cpu().double().numpy(), mr.numpy(), rtol=1e-5)
+                np.testing.assert_allclose(b.invstd.cpu().double().numpy(), sr.numpy(), rtol=1e-5)
+        assert not ex.timed_out()
+    finally:
+        _lib.tune_set("upsample_bnstats_allreduce", -1, 0)
+        _lib.tune_option("exchange_pair_pool", -1)
+        ex.close()
     with pytest.raises(_lib.HfuseError):
         _lib.tune_set_share("upsample_bnstats", 100)          # only the exchange pair has a share
     with pytest.raises(_lib.HfuseError):

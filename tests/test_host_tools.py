@@ -39,6 +39,12 @@ def test_sweep_results_are_written_into_the_default_tables(tmp_path):
     dl = (csrc / "dl_tuned.inc").read_text()
     assert _value(dl, "kDefaultPair_upsample_bnstats_allreduce_wide") == 16
     assert _value(dl, "kDefaultShare_upsample_bnstats_allreduce_wide") == 300
+    share["best"] = {"index": 16, "share_permille": -1, "pool": True}
+    path.write_text(json.dumps(share))
+    apply_tuning.apply_share(str(path), str(csrc))
+    dl = (csrc / "dl_tuned.inc").read_text()
+    assert _value(dl, "kDefaultPool_upsample_bnstats_allreduce") == 1
+    assert _value(dl, "kDefaultPoolPair_upsample_bnstats_allreduce") == 16
     share["n_gpus"], share["best"] = 2, {"index": 20, "share_permille": 100}
     path.write_text(json.dumps(share))
     apply_tuning.apply_share(str(path), str(csrc))
