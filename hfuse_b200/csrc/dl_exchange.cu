@@ -1,9 +1,11 @@
 // Batch-norm statistics whose cross-GPU sum happens INSIDE the kernel, over peer memory:
 // the warp that finishes a channel stores its moments into every rank's exchange buffer with
-// plain 8-byte NVLink stores that carry their own validity tag, then collects every rank's
-// row for that channel and folds them in rank order (dl_roles.cuh, BnXchg).  No collective library call, no second launch; the
-// wait for the other ranks is bounded in time.  In the fused pair the statistics range sends, works through a
-// share of the upsample, and only then collects (fused_share_kernel), so the wait costs nothing.
+// plain NVLink stores whose 8-byte words carry their own validity tag, then collects every rank's
+// row for that channel and folds them in rank order (dl_roles.cuh, BnXchg).  No collective library
+// call, no second launch; the wait for the other ranks is bounded in time.  In the fused pair the
+// statistics range sends, its first warp collects, and all its warps then draw upsample work from the
+// cursor that the upsample range draws from too (fused_pool_kernel), so neither the wait nor the
+// statistics threads' spare time costs anything; fused_share_kernel is the older form with a fixed share.
 // The reference is single-GPU, so none of this has a counterpart there.
 #include "dl_host.cuh"
 
