@@ -530,6 +530,10 @@ def run_ours(args):
             ex = None
     if args.pair_variant >= 0:
         _lib.tune_set("upsample_bnstats_allreduce" if ex is not None else "upsample_bnstats", args.pair_variant, 0)
+
+    def shape_of(pair):      # "T1,T2,minBlocks" of the variant that will run
+        d = _lib.tune_variants(pair)[args.pair_variant] if args.pair_variant >= 0 else _lib.tune_default(pair)
+        return d.replace(":", ",")
     if args.share_permille >= 0 and ex is not None:
         _lib.tune_set_share("upsample_bnstats_allreduce", args.share_permille)
     if args.tune_share:
@@ -537,7 +541,7 @@ def run_ours(args):
     stream = torch.cuda.Stream(dev)          # everything timed runs (and is captured) on this stream
     if ex is not None:
         collective = "in-kernel sum of the [256,3] f64 moments over NVLink peer stores"
-        kernel_name = "fused_pool_kernel<UpsampleRole,BnStatsXchgRole,384,256,2>"
+        kernel_name = "fused_pool_kernel<UpsampleRole,BnStatsXchgRole,%s>" % shape_of("upsample_bnstats_allreduce")
 
         def step(i):
             ex.run_pair(*sets[i % NSETS])
@@ -545,7 +549,7 @@ def run_ours(args):
     elif use_dist:
         # per-GPU moments -> NCCL all-reduce -> finalize kernel, all on the timed stream
         collective = "NCCL all-reduce of the [256,3] f64 moments + finalize kernel"
-        kernel_name = "fused_kernel<UpsampleRole,BnStatsRole,512,256,2>"
+        kernel_name = "fused_kernel<UpsampleRole,BnStatsRole,%s>" % shape_of("upsample_bnstats")
         for a, b in sets:
             b.moments = torch.empty((256, 3), dtype=torch.float64, device=dev)
 
@@ -558,7 +562,7 @@ def run_ours(args):
             b.invstd.copy_(s_)
         per_step_launches = 5
     else:
-        kernel_name = "fused_kernel<UpsampleRole,BnStatsRole,512,256,2>"
+        kernel_name = "fused_kernel<UpsampleRole,BnStatsRole,%s>" % shape_of("upsample_bnstats")
 
         def step(i):
             ops.run_pair(*sets[i % NSETS])
@@ -941,14 +945,16 @@ def run_tune_share(args, torch, _lib, ex, sets, nsets, dev, rank, barrier, use_d
     name = "upsample_bnstats_allreduce"
     descr = _lib.tune_variants(name)
     variants = [v for v, d in enumerate(descr) if ":0:" not in d]
-    shares = (0, 100, 200, 300, 400, 500, "pool")       # "pool": items drawn from a cursor by both ranges
+    # "pool": items drawn from a cursor by both ranges; "pool_bulk": the same with the statistics read through bulk copies
+    shares = (0, 100, 200, 300, 400, 500, "pool", "pool_bulk")
     reps, gsteps = 6, 4 * nsets
     table = {}
     for v in variants:
         row = {}
         for share in shares:
             _lib.tune_set(name, v, 0)
-            if share == "pool":
+            _lib.tune_option("bnstats_load_path", 1 if share == "pool_bulk" else 0)
+            if share in ("pool", "pool_bulk"):
                 _lib.tune_set_share(name, -1)
                 _lib.tune_option("exchange_pair_pool", 1)
             else:
@@ -977,6 +983,7 @@ def run_tune_share(args, torch, _lib, ex, sets, nsets, dev, rank, barrier, use_d
             del graph
         table[descr[v]] = row
     _lib.tune_option("exchange_pair_pool", -1)
+    _lib.tune_option("bnstats_load_path", -1)
     _lib.tune_set(name, -1, 0)
     _lib.tune_set_share(name, -1)
     timed_out = ex.timed_out()
@@ -984,8 +991,9 @@ def run_tune_share(args, torch, _lib, ex, sets, nsets, dev, rank, barrier, use_d
         best = min(((t, d, sh) for d, row in table.items() for sh, t in row.items()))
         print(json.dumps({"pair": name, "n_gpus": args.gpus, "unit": "us per step, max over ranks",
                           "best": {"variant": best[1], "index": descr.index(best[1]),
-                                   "share_permille": -1 if best[2] == "pool" else int(best[2]),
-                                   "pool": best[2] == "pool", "us": best[0]},
+                                   "share_permille": -1 if best[2].startswith("pool") else int(best[2]),
+                                   "pool": best[2].startswith("pool"), "bnstats_bulk": int(best[2] == "pool_bulk"),
+                                   "us": best[0]},
                           "exchange_timed_out": timed_out, "table": table}))
     if use_dist:
         shutdown(torch, None)
@@ -1149,21 +1157,31 @@ def run_tune(args, torch, ops, crypto, workloads, dev):
     steps = 48
 
     def paths_of(name):
-        """Store paths of the im2col role to sweep for this kernel or pair (others have one)."""
-        return (0, 1) if "im2col" in name else (None,)
+        """(store path of the im2col role, load path of the statistics role) combinations to sweep
+        for this kernel or pair; None where the kernel has no such role."""
+        ips = (0, 1) if "im2col" in name else (None,)
+        bps = (0, 1) if "bnstats" in name else (None,)
+        return [(ip, bp) for ip in ips for bp in bps]
+
+    def label(d, path):
+        ip, bp = path
+        return d + ("" if ip is None else f" path{ip}") + ("" if bp is None else f" bn{bp}")
 
     def sweep(name, run_one):
-        """{(path, variant description): us} over every store path and compiled variant."""
+        """{((im2col path, statistics path), variant description): us} over every path and compiled variant."""
         times = {}
         try:
             for path in paths_of(name):
-                if path is not None:
-                    _lib.tune_option("im2col_store_path", path)
+                if path[0] is not None:
+                    _lib.tune_option("im2col_store_path", path[0])
+                if path[1] is not None:
+                    _lib.tune_option("bnstats_load_path", path[1])
                 for v, d in enumerate(_lib.tune_variants(name)):
                     _lib.tune_set(name, v, 0)
                     times[(path, d)] = round(graph_region(torch, run_one, NS, steps, 3) * 1e3, 2)
         finally:
             _lib.tune_option("im2col_store_path", -1)
+            _lib.tune_option("bnstats_load_path", -1)
             _lib.tune_set(name, -1, 0)
         return times
 
@@ -1172,9 +1190,11 @@ def run_tune(args, torch, ops, crypto, workloads, dev):
         cand = {k: t for k, t in times.items() if not (horizontal_only and ":0:" in k[1])}
         (path, d), us = min(cand.items(), key=lambda kv: kv[1])
         out = {"best": descr.index(d), "variant": d, "us": us,
-               "all": {(d2 if p is None else f"{d2} path{p}"): t for (p, d2), t in times.items()}}
-        if path is not None:
-            out["im2col_bulk"] = path
+               "all": {label(d2, p): t for (p, d2), t in times.items()}}
+        if path[0] is not None:
+            out["im2col_bulk"] = path[0]
+        if path[1] is not None:
+            out["bnstats_bulk"] = path[1]
         return out, path
 
     for key in _lib.DL_SOLO:
@@ -1185,8 +1205,10 @@ def run_tune(args, torch, ops, crypto, workloads, dev):
         out, path = describe(times, key, False)
         result["solo"][key] = out
         _lib.tune_set(key, out["best"], 0)       # keep the best standalone for the b2b baseline
-        if path is not None:
-            solo_im2col_path = path
+        if path[0] is not None:
+            solo_im2col_path = path[0]
+        if path[1] is not None:
+            solo_bn_path = path[1]
         del sets
         torch.cuda.empty_cache()
     for name, (ka, kb) in _lib.DL_PAIRS.items():
@@ -1194,6 +1216,8 @@ def run_tune(args, torch, ops, crypto, workloads, dev):
         sets = [(mk(ka, big), mk(kb, big)) for _ in range(NS)]
         if "im2col" in name:                     # the baseline's standalone im2col takes ITS best path
             _lib.tune_option("im2col_store_path", solo_im2col_path)
+        if "bnstats" in name:                    # and so does the standalone statistics kernel
+            _lib.tune_option("bnstats_load_path", solo_bn_path)
         t_b2b = graph_region(torch, lambda i: ops.run_back_to_back(*sets[i % NS]), NS, steps, 3) * 1e3
         times = sweep(name, lambda i: ops.run_pair(*sets[i % NS]))
         out, _ = describe(times, name, True)
@@ -1207,10 +1231,12 @@ def run_tune(args, torch, ops, crypto, workloads, dev):
     if args.tune_skip_crypto:
         print(json.dumps(result))
         return
-    # crypto: reduced sweeps (2^27 nonces for the ALU hashes, 2^23 for ethash and for whatever
-    # is paired with ethash: the benchmark configurations give both halves the same count)
+    # crypto: reduced sweeps, 2^27 nonces (the benchmark configurations give both halves the same
+    # count).  For ethash and its partners that is 0.2 s per launch: long enough for the board to reach
+    # its power cap, under which the 2^30-nonce benchmark sweeps run; the best block shapes under the cap
+    # are not the best ones of a few milliseconds.
     c3, c4 = workloads.config3(), workloads.config4(dev)
-    NA, NE = 1 << 27, 1 << 23
+    NA, NE = 1 << 27, 1 << 27
 
     def mkc(key, n=None):
         if key == "blake256":

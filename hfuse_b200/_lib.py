@@ -71,7 +71,7 @@ def exported_symbols() -> list[str]:
     names += ["hfuse_maxpool2d_backward_f32", "hfuse_bn_backward_f32", "hfuse_maxpool_backward_bn_backward_f32"]
     names += ["hfuse_error_string", "hfuse_version", "hfuse_bnstats_workspace_bytes", "hfuse_bnstats_noalloc_f32",
               "hfuse_bnstats_finalize_f64", "hfuse_hits_reset", "hfuse_hash_batch", "hfuse_tune_set",
-              "hfuse_tune_describe", "hfuse_tune_set_share", "hfuse_tune_option", "hfuse_xoshiro256ss_fill", "hfuse_int32_probe", "hfuse_hbm_probe", "hfuse_hbm_probe_bulk", "hfuse_shard_range"]
+              "hfuse_tune_describe", "hfuse_tune_default", "hfuse_tune_set_share", "hfuse_tune_option", "hfuse_xoshiro256ss_fill", "hfuse_int32_probe", "hfuse_hbm_probe", "hfuse_hbm_probe_bulk", "hfuse_shard_range"]
     return names
 
 
@@ -152,6 +152,7 @@ def lib() -> C.CDLL:
     L.hfuse_tune_describe.restype, L.hfuse_tune_describe.argtypes = _i, [C.c_char_p, _i, C.c_char_p, _sz]
     L.hfuse_tune_set_share.restype, L.hfuse_tune_set_share.argtypes = _i, [C.c_char_p, _i]
     L.hfuse_tune_option.restype, L.hfuse_tune_option.argtypes = _i, [C.c_char_p, _i]
+    L.hfuse_tune_default.restype, L.hfuse_tune_default.argtypes = _i, [C.c_char_p]
     L.hfuse_xoshiro256ss_fill.restype, L.hfuse_xoshiro256ss_fill.argtypes = None, [_u64, _p, _sz]
     L.hfuse_shard_range.restype = _i
     L.hfuse_shard_range.argtypes = [_u64, _i, _i, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
@@ -181,6 +182,13 @@ def tune_set_share(name: str, permille: int = -1) -> None:
 
 def tune_option(name: str, value: int) -> None:
     check(lib().hfuse_tune_option(name.encode(), value), f"tune_option({name})")
+
+
+def tune_default(name: str) -> str:
+    """Descriptor ("T1:T2:minBlocks") of the compiled default variant of a kernel or pair."""
+    v = lib().hfuse_tune_default(name.encode())
+    check(min(v, 0), f"tune_default({name})")
+    return tune_variants(name)[v]
 
 
 def tune_variants(name: str) -> list[str]:

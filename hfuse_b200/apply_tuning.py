@@ -41,6 +41,9 @@ def apply(path: str, csrc: str = CSRC) -> None:
                 if "im2col_bulk" in entry:       # store path of the im2col role in this kernel / pair
                     src, n = re.subn(rf"(kIm2colBulk_{name} = )\d+;", rf"\g<1>{int(entry['im2col_bulk'])};", src)
                     assert n == 1, name
+                if "bnstats_bulk" in entry:      # load path of the statistics role in this kernel / pair
+                    src, n = re.subn(rf"(kBnStatsBulk_{name} = )\d+;", rf"\g<1>{int(entry['bnstats_bulk'])};", src)
+                    assert n == 1, name
         open(p, "w").write(src)
         print("updated", p)
 
@@ -56,7 +59,8 @@ def apply_share(path: str, csrc: str = CSRC) -> None:
     src = open(p).read()
     if res["best"].get("pool"):       # the cursor form won: one thread split for any number of ranks
         pairs = (("kDefaultPool_upsample_bnstats_allreduce", 1),
-                 ("kDefaultPoolPair_upsample_bnstats_allreduce", res["best"]["index"]))
+                 ("kDefaultPoolPair_upsample_bnstats_allreduce", res["best"]["index"]),
+                 ("kBnStatsBulk_upsample_bnstats_allreduce", res["best"].get("bnstats_bulk", 0)))
     else:
         pairs = ((f"kDefaultPair_upsample_bnstats_allreduce{suffix}", res["best"]["index"]),
                  (f"kDefaultShare_upsample_bnstats_allreduce{suffix}", res["best"]["share_permille"]))

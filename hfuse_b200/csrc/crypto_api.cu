@@ -85,6 +85,10 @@ int crypto_describe(const char* name, int variant, char* buf, size_t n) {
     case I: snprintf(buf, n, "%d:0:%d", T, MB); return kCryptoSoloVariants;
                 CRYPTO_SOLO_VARIANTS(X)
 #undef X
+#define X(I, T, MB) \
+    case I: snprintf(buf, n, "%d:0:%d queue", T, MB); return kCryptoSoloVariants;
+                CRYPTO_SOLO_QUEUE_VARIANTS(X)
+#undef X
             }
             return HFUSE_ERR_BAD_ARG;
         }
@@ -98,6 +102,14 @@ int crypto_describe(const char* name, int variant, char* buf, size_t n) {
             }
             return HFUSE_ERR_BAD_ARG;
         }
+    return HFUSE_ERR_UNKNOWN_PAIR;
+}
+int crypto_default_variant(const char* name) {
+#define D(kind, n) if (!strcmp(name, #n)) return kDefault##kind##_##n;
+    D(Solo, blake256) D(Solo, sha256d) D(Solo, sia) D(Solo, ethash)
+    D(Pair, ethash_blake256) D(Pair, sha256d_ethash) D(Pair, sia_ethash) D(Pair, blake256_sha256d)
+    D(Pair, blake256_sia) D(Pair, sha256d_sia)
+#undef D
     return HFUSE_ERR_UNKNOWN_PAIR;
 }
 }  // namespace hfuse

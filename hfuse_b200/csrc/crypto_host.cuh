@@ -140,7 +140,10 @@ int prep_eth(HFUSE_ETHASH_PARAMS(), EthashArgs& a) {
 constexpr int kCryptoPairVariants = 20;
 #define CRYPTO_SOLO_VARIANTS(X) \
     X(0, 128, 4) X(1, 128, 6) X(2, 128, 8) X(3, 256, 2) X(4, 256, 3) X(5, 256, 4) X(6, 128, 3) X(7, 128, 5) X(8, 128, 2)
-constexpr int kCryptoSoloVariants = 9;
+// the same sweep in work-queue form (warps draw chunks of nonces from the cursor in the hits record)
+#define CRYPTO_SOLO_QUEUE_VARIANTS(X) \
+    X(9, 256, 3) X(10, 384, 2) X(11, 128, 6) X(12, 256, 2) X(13, 192, 4) X(14, 512, 1)
+constexpr int kCryptoSoloVariants = 15;
 
 template <class RA, class RB>
 int dispatch_pair(const char* name, int default_variant, typename RA::Args a, typename RB::Args b, cudaStream_t s) {
@@ -167,6 +170,12 @@ int dispatch_solo(const char* name, int default_variant, typename R::Args a, cud
 #define X(I, T, MB) \
     case I: return launch_solo<R, T, MB>(a, t.blocks_per_sm, s);
         CRYPTO_SOLO_VARIANTS(X)
+#undef X
+#define X(I, T, MB)                                                                                         \
+    case I:                                                                                                 \
+        if (cudaMemsetAsync(&a.c.hits->reserved, 0, sizeof(uint32_t), s) != cudaSuccess) return HFUSE_ERR_LAUNCH; \
+        return launch_solo_queue<R, T, MB>(a, t.blocks_per_sm, s);
+        CRYPTO_SOLO_QUEUE_VARIANTS(X)
 #undef X
     }
     return HFUSE_ERR_BAD_ARG;

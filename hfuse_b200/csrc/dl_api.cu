@@ -72,4 +72,17 @@ int dl_describe(const char* name, int variant, char* buf, size_t n) {
         if (!strcmp(p, name)) return describe_dl_pair(variant, buf, n);
     return HFUSE_ERR_UNKNOWN_PAIR;
 }
+// compiled default variant of a DL kernel or pair (for the exchange pair: of its cursor form when that is the default form)
+int dl_default_variant(const char* name) {
+#define D(kind, n) if (!strcmp(name, #n)) return kDefault##kind##_##n;
+    D(Solo, im2col) D(Solo, maxpool) D(Solo, bnstats) D(Solo, upsample) D(Solo, histc)
+    D(Pair, im2col_maxpool) D(Pair, im2col_bnstats) D(Pair, im2col_histc) D(Pair, im2col_upsample)
+    D(Pair, maxpool_bnstats) D(Pair, maxpool_upsample) D(Pair, histc_maxpool) D(Pair, histc_upsample)
+    D(Pair, upsample_bnstats) D(Pair, histc_bnstats)
+#undef D
+    if (!strcmp(name, "upsample_bnstats_allreduce"))
+        return kDefaultPool_upsample_bnstats_allreduce == 1 ? kDefaultPoolPair_upsample_bnstats_allreduce
+                                                            : kDefaultPair_upsample_bnstats_allreduce;
+    return HFUSE_ERR_UNKNOWN_PAIR;
+}
 }  // namespace hfuse

@@ -105,6 +105,18 @@ int prep_bnstats(HFUSE_BNSTATS_PARAMS(), BnStatsArgs& a) {
     a.vec = (HW % 4) == 0;
     a.ws = workspace; a.ws_bytes = workspace_bytes;
     a.xchg = BnXchg{};
+    // bulk-load path: rows of 1 to 25 KB that are 16-byte multiples; as few, equally long buffer fills as fit 25 KB
+    // bulk-load path: rows of 1 to 25 KB that are 16-byte multiples; three buffers, each holding as many rows
+    // as fit 25 KB, all fills of a channel equally long (measured on B200: two to four buffers of 12.5 or 25 KB
+    // are within 0.3 us of each other; alone or with a large statistics range the register path is faster)
+    a.bulk = 0; a.bulk_ok = 0; a.bulk_rows = 1; a.bulk_bufs = 3;
+    const long long row_bytes = (long long)HW * 4;
+    if (a.vec && row_bytes >= 1024 && row_bytes <= 25600) {
+        const int rmax = (int)(25600 / row_bytes);
+        const int fills = (N + rmax - 1) / rmax;
+        a.bulk_rows = (unsigned)((N + fills - 1) / fills);
+        a.bulk_ok = 1;
+    }
     return HFUSE_OK;
 }
 
@@ -175,6 +187,13 @@ void choose_path(Im2colArgs& a, const char* name) {
     const int opt = option_get("im2col_store_path", -1);
     if (opt >= 0 ? opt == 1 : default_im2col_bulk(name) == 1) a.mode = 3;
 }
+// The same for the statistics role's load path (option "bnstats_load_path").
+int default_bnstats_bulk(const char* name);
+void choose_path(BnStatsArgs& a, const char* name) {
+    if (!a.bulk_ok) return;
+    const int opt = option_get("bnstats_load_path", -1);
+    a.bulk = (opt >= 0 ? opt == 1 : default_bnstats_bulk(name) == 1) ? 1 : 0;
+}
 template <class A> void choose_path(A&, const char*) {}
 
 // pre_launch returns a negative error, 0, or 1 when the main kernel must be launched as the
@@ -232,6 +251,8 @@ int dispatch_pair_share(const char* name, int default_variant, int default_share
     const Tune t = tune_get(name);
     const int v = t.variant >= 0 ? t.variant : default_variant;
     const int share = t.share_permille >= 0 ? t.share_permille : default_share;
+    choose_path(a, name);
+    choose_path(b, name);
     const int pa = pre_launch(a, s), pb = pre_launch(b, s);
     if (pa < 0) return pa;
     if (pb < 0) return pb;
@@ -254,6 +275,8 @@ template <class RA, class RB>
 int dispatch_pair_pool(const char* name, int default_variant, typename RA::Args a, typename RB::Args b, cudaStream_t s) {
     const Tune t = tune_get(name);
     const int v = t.variant >= 0 ? t.variant : default_variant;
+    choose_path(a, name);
+    choose_path(b, name);
     const int pa = pre_launch(a, s), pb = pre_launch(b, s);
     if (pa < 0) return pa;
     if (pb < 0) return pb;
@@ -313,6 +336,16 @@ int describe_dl_solo(int v, char* buf, size_t n) {
 // default variant per kernel / pair (index into the lists above), chosen by the sweep
 // in bench.py --tune on a B200
 #include "dl_tuned.inc"
+
+int default_bnstats_bulk(const char* name) {
+    if (!strcmp(name, "bnstats")) return kBnStatsBulk_bnstats;
+    if (!strcmp(name, "im2col_bnstats")) return kBnStatsBulk_im2col_bnstats;
+    if (!strcmp(name, "maxpool_bnstats")) return kBnStatsBulk_maxpool_bnstats;
+    if (!strcmp(name, "upsample_bnstats")) return kBnStatsBulk_upsample_bnstats;
+    if (!strcmp(name, "histc_bnstats")) return kBnStatsBulk_histc_bnstats;
+    if (!strcmp(name, "upsample_bnstats_allreduce")) return kBnStatsBulk_upsample_bnstats_allreduce;
+    return 0;
+}
 
 int default_im2col_bulk(const char* name) {
     if (!strcmp(name, "im2col")) return kIm2colBulk_im2col;

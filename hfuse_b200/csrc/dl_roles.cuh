@@ -927,9 +927,14 @@ struct BnStatsArgs {
     size_t ws_bytes;      // size of the caller's scratch buffer (host-side check only)
     void* ws;             // the caller's scratch buffer
     BnXchg xchg;          // world == 0 unless launched through an exchange entry point
+    int bulk_ok;          // the shape allows the bulk-load path (16-byte rows of 1 to 24 KB)
+    int bulk;             // 1: channels are brought into shared memory by bulk (TMA) copies (run_bulk)
+    unsigned bulk_rows;   // image rows of one channel per shared-memory buffer on that path
+    unsigned bulk_bufs;   // buffers in the ring (2 .. kBnBulkMaxBufs)
 };
 
 constexpr int kBnMaxSlices = 256;
+constexpr int kBnBulkMaxBufs = 4;
 inline size_t bn_ticket_bytes(int C) { return (((size_t)C * sizeof(unsigned)) + 255) & ~(size_t)255; }
 inline size_t bn_workspace_bytes(int C) {
     return bn_ticket_bytes(C) + (size_t)C * kBnMaxSlices * 3 * sizeof(float);
@@ -965,8 +970,11 @@ __device__ __forceinline__ Moments warp_merge(Moments m) {
 
 struct BnStatsRole {
     using Args = BnStatsArgs;
-    // two parity buffers of per-warp moments
-    static int smem_bytes(const Args&, int T) { return 2 * 3 * (T / 32) * (int)sizeof(float); }
+    // two parity buffers of per-warp moments; on the bulk-load path two mbarriers and two tile buffers behind them
+    static __host__ __device__ __forceinline__ int moments_bytes(int T) { return (2 * 3 * (T / 32) * (int)sizeof(float) + 15) & ~15; }
+    static int smem_bytes(const Args& a, int T) {
+        return moments_bytes(T) + (a.bulk ? kBnBulkMaxBufs * 8 + (int)a.bulk_bufs * (int)a.bulk_rows * a.HW * (int)sizeof(float) : 0);
+    }
 
     // One channel per unit when the channels alone give every block work;
     // otherwise S slices per channel, but never fewer than two loads per thread in a slice.
@@ -982,6 +990,7 @@ struct BnStatsRole {
         a.div_img = make_fastdiv(a.per_img);
         a.chunk = (unsigned)((per_channel + S - 1) / S);
         a.S = (int)((per_channel + a.chunk - 1) / a.chunk);
+        if (a.S != 1) a.bulk = 0;      // the bulk-load path works on whole channels
         if (a.S > 1) {
             if (a.ws == nullptr || a.ws_bytes < bn_workspace_bytes(a.C)) return -4;   // HFUSE_ERR_WORKSPACE
             a.tickets = reinterpret_cast<unsigned*>(a.ws);
@@ -1094,14 +1103,133 @@ struct BnStatsRole {
         for (unsigned u = ctx.block; u < (unsigned)a.C; u += ctx.nblocks) xchg_collect(a, use, (int)u, ctx.tid & 31);
     }
 
-    // `word`: the block's check-in word (XCHG only; held by thread 0, see xchg_check_in)
+    // The end of a unit, entered by all T threads with their shifted sums: per-thread moments, warp
+    // fold, the role-wide fold through shared memory behind the role's barrier, then warp 0 finishes
+    // the channel (or publishes the slice and, on the last ticket, folds all slices).
     template <int T, int BAR, bool XCHG, bool DEFER>
-    static __device__ __forceinline__ void run_impl(const Args& a, const RoleCtx& ctx, unsigned long long word = 0ull) {
+    static __device__ __forceinline__ void fold_unit(const Args& a, const RoleCtx& ctx, unsigned long long word, int parity,
+                                                     unsigned c, unsigned s, float cnt, float sum, float sq, float shift) {
         constexpr int NW = T / 32;
-        constexpr int UNROLL = 4;      // 16-byte loads in flight per thread and trip (8 was measured: 0.4 us off the standalone kernel, spills in the 40-register pair shapes)
         static_assert(NW <= 32, "one warp folds the per-warp moments");
         float* sh = reinterpret_cast<float*>(ctx.smem);
         const int lane = ctx.tid & 31, warp = ctx.tid >> 5;
+        Moments m{0.f, 0.f, 0.f};
+        if (cnt > 0.f) {
+            const float dm = sum / cnt;
+            m = Moments{cnt, shift + dm, fmaxf(sq - sum * dm, 0.f)};
+        }
+        m = warp_merge(m);
+        float* buf = sh + parity * 3 * NW;
+        if (lane == 0) { buf[warp] = m.n; buf[NW + warp] = m.mean; buf[2 * NW + warp] = m.m2; }
+        role_sync<BAR, T>();
+        // The parity buffer keeps warp 0's reads of this unit apart from the next unit's
+        // writes; the unit after that is fenced by the next barrier.
+        if (warp != 0) return;
+        Moments w = (lane < NW) ? Moments{buf[lane], buf[NW + lane], buf[2 * NW + lane]} : Moments{0.f, 0.f, 0.f};
+        w = warp_merge(w);
+        XchgUse use{0u, 0u};
+        if (XCHG) use = xchg_use(__shfl_sync(0xffffffffu, word, 0));     // warp 0: thread 0 holds the word
+        if (a.S == 1) {
+            complete<XCHG, DEFER>(a, use, (int)c, w, lane);
+            return;
+        }
+        // publish this slice; the block that takes the last ticket folds all slices
+        unsigned ticket = 0;
+        if (lane == 0) {
+            float* p = a.partial + ((size_t)c * a.S + s) * 3;
+            __stcg(p, w.n); __stcg(p + 1, w.mean); __stcg(p + 2, w.m2);
+            __threadfence();
+            ticket = atomicAdd(a.tickets + c, 1u);
+        }
+        ticket = __shfl_sync(0xffffffffu, ticket, 0);
+        if (ticket == (unsigned)(a.S - 1)) {
+            __threadfence();
+            Moments q{0.f, 0.f, 0.f};
+            for (int i = lane; i < a.S; i += 32) {      // fixed order: lane, lane+32, ...
+                const float* p = a.partial + ((size_t)c * a.S + i) * 3;
+                q = chan_merge(q, Moments{__ldcg(p), __ldcg(p + 1), __ldcg(p + 2)});
+            }
+            q = warp_merge(q);
+            if (lane == 0) a.tickets[c] = 0u;     // ready for the next call
+            complete<XCHG, false>(a, use, (int)c, q, lane);
+        }
+    }
+
+    // Bulk-load path (one slice per channel, rows of HW floats that are 16-byte multiples): the
+    // channel's N rows come into shared memory through bulk (TMA) copies, `bulk_rows` rows per
+    // buffer, a ring of `bulk_bufs` buffers, each with an mbarrier that counts the bytes landed.
+    // One thread issues the copies, so the loads in flight cost no registers and do not depend on
+    // how many threads the role has; all T threads then sum a buffer from shared memory while the
+    // others are on their way.  A buffer is refilled after the role's barrier that follows its
+    // last reader.
+    template <int T, int BAR, bool XCHG, bool DEFER>
+    static __device__ __forceinline__ void run_bulk(const Args& a, const RoleCtx& ctx, unsigned long long word) {
+        unsigned char* base = ctx.smem + moments_bytes(T);
+        unsigned long long* full = reinterpret_cast<unsigned long long*>(base);      // one barrier per buffer
+        unsigned char* tiles = base + kBnBulkMaxBufs * 8;
+        const unsigned row_bytes = (unsigned)a.HW * (unsigned)sizeof(float), row4 = (unsigned)a.HW >> 2;
+        const unsigned R = a.bulk_rows, rows = (unsigned)a.N, NB = a.bulk_bufs;
+        const unsigned buf_bytes = R * row_bytes;
+        const unsigned nfill = (rows + R - 1) / R;         // buffer fills per channel
+        const size_t img_stride = (size_t)a.C * a.HW;
+        constexpr unsigned long long kTimeoutNs = 2000000000ull;
+        if (ctx.tid == 0) {
+            for (unsigned b = 0; b < NB; ++b) mbar_init(full + b, 1u);
+            fence_mbar_init();
+        }
+        role_sync<BAR, T>();
+        unsigned used = 0;            // buffer fills consumed so far; every thread counts alike
+        int parity = 0;
+        bool ok = true;
+        for (unsigned u = ctx.block; u < (unsigned)a.C; u += ctx.nblocks, parity ^= 1) {
+            const float* xc = a.x + (size_t)u * a.HW;
+            auto issue = [&](unsigned k, unsigned f) {      // rows [k*R, k*R + n) of channel u as fill number f
+                const unsigned n = min(R, rows - k * R), slot = f % NB;
+                mbar_expect_tx(full + slot, n * row_bytes);
+                unsigned char* dst = tiles + (size_t)slot * buf_bytes;
+                for (unsigned r = 0; r < n; ++r)
+                    bulk_load(dst + (size_t)r * row_bytes, xc + (size_t)(k * R + r) * img_stride, row_bytes, full + slot);
+            };
+            // every thread is past its last read of all buffers (the previous unit ended with the role's barrier)
+            if (ctx.tid == 0)
+                for (unsigned k = 0; k < NB && k < nfill; ++k) issue(k, used + k);
+            float cnt = 0.f, sum = 0.f, sq = 0.f, shift = 0.f;
+            for (unsigned k = 0; k < nfill; ++k, ++used) {
+                const unsigned slot = used % NB, par = (used / NB) & 1u;
+                ok &= mbar_wait(full + slot, par, kTimeoutNs);
+                const unsigned items = min(R, rows - k * R) * row4;
+                const float4* t = reinterpret_cast<const float4*>(tiles + (size_t)slot * buf_bytes);
+                for (unsigned i = ctx.tid; i < items; i += T) {
+                    const float4 v = t[i];
+                    if (cnt == 0.f) shift = v.x;
+                    const float d0 = v.x - shift, d1 = v.y - shift, d2 = v.z - shift, d3 = v.w - shift;
+                    sum += (d0 + d1) + (d2 + d3);
+                    sq = fmaf(d0, d0, fmaf(d1, d1, fmaf(d2, d2, fmaf(d3, d3, sq))));
+                    cnt += 4.f;
+                }
+                if (k + NB < nfill) {
+                    role_sync<BAR, T>();
+                    if (ctx.tid == 0) issue(k + NB, used + NB);
+                }
+            }
+            // a wait that ran out of time: the statistics of this channel come out as NaN
+            if (!__all_sync(0xffffffffu, ok)) sum = __int_as_float(0x7fc00000);
+            fold_unit<T, BAR, XCHG, DEFER>(a, ctx, word, parity, u, 0u, cnt, sum, sq, shift);
+        }
+        // thread 0 is past the last fold's barrier, so nobody waits on the barriers any more: give
+        // their shared memory back (a vertically fused partner reuses it)
+        if (ctx.tid == 0)
+            for (unsigned b = 0; b < NB; ++b) mbar_inval(full + b);
+    }
+
+    // `word`: the block's check-in word (XCHG only; held by thread 0, see xchg_check_in)
+    template <int T, int BAR, bool XCHG, bool DEFER>
+    static __device__ __forceinline__ void run_impl(const Args& a, const RoleCtx& ctx, unsigned long long word = 0ull) {
+        if (a.bulk) {
+            run_bulk<T, BAR, XCHG, DEFER>(a, ctx, word);
+            return;
+        }
+        constexpr int UNROLL = 4;      // 16-byte loads in flight per thread and trip (8 was measured: 0.4 us off the standalone kernel, spills in the 40-register pair shapes)
         const unsigned units = (unsigned)a.C * (unsigned)a.S;
         int parity = 0;
         for (unsigned u = ctx.block; u < units; u += ctx.nblocks, parity ^= 1) {
@@ -1159,47 +1287,7 @@ struct BnStatsRole {
                     }
                 }
             }
-            Moments m{0.f, 0.f, 0.f};
-            if (cnt > 0.f) {
-                const float dm = sum / cnt;
-                m = Moments{cnt, shift + dm, fmaxf(sq - sum * dm, 0.f)};
-            }
-            // ---- warp fold, then the role-wide fold through shared memory and the role's barrier
-            m = warp_merge(m);
-            float* buf = sh + parity * 3 * NW;
-            if (lane == 0) { buf[warp] = m.n; buf[NW + warp] = m.mean; buf[2 * NW + warp] = m.m2; }
-            role_sync<BAR, T>();
-            // The parity buffer keeps warp 0's reads of this unit apart from the next unit's
-            // writes; the unit after that is fenced by the next barrier.
-            if (warp != 0) continue;
-            Moments w = (lane < NW) ? Moments{buf[lane], buf[NW + lane], buf[2 * NW + lane]} : Moments{0.f, 0.f, 0.f};
-            w = warp_merge(w);
-            XchgUse use{0u, 0u};
-            if (XCHG) use = xchg_use(__shfl_sync(0xffffffffu, word, 0));     // warp 0: thread 0 holds the word
-            if (a.S == 1) {
-                complete<XCHG, DEFER>(a, use, (int)c, w, lane);
-                continue;
-            }
-            // publish this slice; the block that takes the last ticket folds all slices
-            unsigned ticket = 0;
-            if (lane == 0) {
-                float* p = a.partial + ((size_t)c * a.S + s) * 3;
-                __stcg(p, w.n); __stcg(p + 1, w.mean); __stcg(p + 2, w.m2);
-                __threadfence();
-                ticket = atomicAdd(a.tickets + c, 1u);
-            }
-            ticket = __shfl_sync(0xffffffffu, ticket, 0);
-            if (ticket == (unsigned)(a.S - 1)) {
-                __threadfence();
-                Moments q{0.f, 0.f, 0.f};
-                for (int i = lane; i < a.S; i += 32) {      // fixed order: lane, lane+32, ...
-                    const float* p = a.partial + ((size_t)c * a.S + i) * 3;
-                    q = chan_merge(q, Moments{__ldcg(p), __ldcg(p + 1), __ldcg(p + 2)});
-                }
-                q = warp_merge(q);
-                if (lane == 0) a.tickets[c] = 0u;     // ready for the next call
-                complete<XCHG, false>(a, use, (int)c, q, lane);
-            }
+            fold_unit<T, BAR, XCHG, DEFER>(a, ctx, word, parity, c, s, cnt, sum, sq, shift);
         }
     }
 };

@@ -21,6 +21,13 @@ __global__ void __launch_bounds__(T, MINB) solo_kernel(const __grid_constant__ t
     Role::template run<T, 1>(a, ctx);
 }
 
+// One work-queue role over the whole block (the nonce searches): every warp draws chunks of nonces
+// from the role's cursor until the range is used up, instead of walking a fixed grid-stride share.
+template <class Role, int T, int MINB>
+__global__ void __launch_bounds__(T, MINB) solo_queue_kernel(const __grid_constant__ typename Role::Args a, unsigned chunk) {
+    Role::drain(a, chunk);
+}
+
 template <class RoleA, class RoleB, int TA, int TB, int MINB>
 __global__ void __launch_bounds__(TA + TB, MINB)
 fused_kernel(const __grid_constant__ typename RoleA::Args a, const __grid_constant__ typename RoleB::Args b,

@@ -6,6 +6,8 @@
 namespace hfuse {
 int dl_describe(const char* name, int variant, char* buf, size_t n);
 int crypto_describe(const char* name, int variant, char* buf, size_t n);
+int dl_default_variant(const char* name);
+int crypto_default_variant(const char* name);
 }  // namespace hfuse
 
 extern "C" {
@@ -36,6 +38,13 @@ int hfuse_tune_describe(const char* pair, int variant, char* buf, size_t buflen)
     return rc;
 }
 
+int hfuse_tune_default(const char* pair) {
+    if (!pair) return HFUSE_ERR_BAD_ARG;
+    int rc = hfuse::dl_default_variant(pair);
+    if (rc == HFUSE_ERR_UNKNOWN_PAIR) rc = hfuse::crypto_default_variant(pair);
+    return rc;
+}
+
 int hfuse_tune_set(const char* pair, int variant, int blocks_per_sm) {
     if (!pair || blocks_per_sm < 0) return HFUSE_ERR_BAD_ARG;
     if (variant >= 0) {
@@ -63,7 +72,8 @@ int hfuse_tune_set_share(const char* pair, int permille) {
 
 int hfuse_tune_option(const char* name, int value) {
     if (!name) return HFUSE_ERR_BAD_ARG;
-    if (strcmp(name, "im2col_store_path") != 0 && strcmp(name, "exchange_pair_pool") != 0) return HFUSE_ERR_UNKNOWN_PAIR;
+    if (strcmp(name, "im2col_store_path") != 0 && strcmp(name, "exchange_pair_pool") != 0 &&
+        strcmp(name, "bnstats_load_path") != 0) return HFUSE_ERR_UNKNOWN_PAIR;
     if (value < -1 || value > 1) return HFUSE_ERR_BAD_ARG;
     std::lock_guard<std::mutex> lk(hfuse::tune_mutex());
     if (value < 0) hfuse::option_table().erase(name);

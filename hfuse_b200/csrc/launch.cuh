@@ -40,8 +40,24 @@ inline int device_facts(DeviceFacts& out) {
     return HFUSE_OK;
 }
 
-// resident blocks per SM of (kernel, block size, dynamic smem) on the current device
+// more than 48 KB of dynamic shared memory has to be asked for once per kernel and device
+inline void allow_dynamic_smem(const void* func, size_t smem) {
+    if (smem <= 48 * 1024) return;
+    static std::mutex mu;
+    static std::map<std::pair<int, const void*>, size_t> granted;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(mu);
+    size_t& g = granted[{dev, func}];
+    if (g >= smem) return;
+    if (cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess) g = smem;
+    else (void)cudaGetLastError();
+}
+
+// resident blocks per SM of (kernel, block size, dynamic smem) on the current device; the occupancy
+// query only counts shared memory that the kernel has been allowed, so that comes first
 inline int resident_blocks(const void* func, int block, size_t smem) {
+    allow_dynamic_smem(func, smem);
     static std::mutex mu;
     static std::map<std::tuple<int, const void*, int, size_t>, int> cache;
     int dev = 0;
@@ -84,6 +100,8 @@ inline Tune tune_get(const char* name) {
 // "exchange_pair_pool": -1 (unset) = the compiled choice, 1 = the exchange pair draws the upsample's
 // items from a cursor shared by both thread ranges (fused_pool_kernel), 0 = it hands a fixed share
 // of them to the statistics range (fused_share_kernel, hfuse_tune_set_share).
+// "bnstats_load_path": -1 (unset) = the compiled choice of each kernel and pair, 0 = 16-byte loads into
+// registers everywhere, 1 = bulk (TMA) copies into shared memory wherever the shape allows it.
 inline std::map<std::string, int>& option_table() {
     static std::map<std::string, int> t;
     return t;
@@ -92,20 +110,6 @@ inline int option_get(const char* name, int unset) {
     std::lock_guard<std::mutex> lk(tune_mutex());
     auto it = option_table().find(name);
     return it == option_table().end() ? unset : it->second;
-}
-
-// more than 48 KB of dynamic shared memory has to be asked for once per kernel and device
-inline void allow_dynamic_smem(const void* func, size_t smem) {
-    if (smem <= 48 * 1024) return;
-    static std::mutex mu;
-    static std::map<std::pair<int, const void*>, size_t> granted;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    std::lock_guard<std::mutex> lk(mu);
-    size_t& g = granted[{dev, func}];
-    if (g >= smem) return;
-    if (cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess) g = smem;
-    else (void)cudaGetLastError();
 }
 
 inline int check_launch() { return cudaGetLastError() == cudaSuccess ? HFUSE_OK : HFUSE_ERR_LAUNCH; }
@@ -240,6 +244,17 @@ inline unsigned queue_chunk(unsigned long long count, long long warps) {
     const unsigned long long floor_c = (count >> 30) + 1;
     if (c < floor_c) c = floor_c;
     return (unsigned)((c + 31) / 32 * 32);
+}
+
+template <class R, int T, int MINB>
+int launch_solo_queue(typename R::Args a, int blocks_per_sm, cudaStream_t s) {
+    DeviceFacts f;
+    if (int rc = device_facts(f)) return rc;
+    auto kern = solo_queue_kernel<R, T, MINB>;
+    const int bps = blocks_per_sm > 0 ? blocks_per_sm : resident_blocks((const void*)kern, T, 0);
+    const int grid = f.sms * bps;
+    kern<<<grid, T, 0, s>>>(a, queue_chunk(a.c.count, (long long)grid * (T / 32)));
+    return check_launch();
 }
 
 template <class RA, class RB, int TA, int TB, int MINB>

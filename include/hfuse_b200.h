@@ -348,6 +348,9 @@ HFUSE_API int hfuse_sia_ethash_search_sharded(HFUSE_SIA_PARAMS(a_), HFUSE_ETHASH
  * ------------------------------------------------------------------------------------- */
 HFUSE_API int hfuse_tune_set(const char* pair, int variant, int blocks_per_sm);
 HFUSE_API int hfuse_tune_describe(const char* pair, int variant, char* buf, size_t buflen);
+/* Index of the compiled default variant of a kernel or pair (what runs while hfuse_tune_set has
+ * not chosen another one), or HFUSE_ERR_UNKNOWN_PAIR. */
+HFUSE_API int hfuse_tune_default(const char* pair);
 /* "upsample_bnstats_allreduce" only: per mille (0..1000, -1 = compiled default) of the upsample's
  * items that the statistics thread range takes over between sending its moments to the peers and
  * waiting for theirs.  Any other name: HFUSE_ERR_UNKNOWN_PAIR. */
@@ -359,6 +362,11 @@ HFUSE_API int hfuse_tune_set_share(const char* pair, int permille);
  *       through a shared-memory tile and the taps leave as bulk (TMA) copies of whole bands of
  *       rows; -1 (the default) = whichever the sweep on B200 found faster for the kernel or pair
  *       that is called.  Same bytes either way.
+ *   "bnstats_load_path": how the statistics role reads its input when one block handles a whole
+ *       channel and the rows of one image (HW floats) are 1 to 25 KB long and 16-byte multiples.
+ *       0 = 16-byte loads into registers; 1 = bulk (TMA) copies of whole rows into two
+ *       shared-memory buffers, completion counted on an mbarrier, summed from shared memory;
+ *       -1 (the default) = the compiled choice per kernel or pair.  Same statistics to rounding.
  *   "exchange_pair_pool": how hfuse_upsample_bnstats_allreduce_f32 divides the upsample between its
  *       two thread ranges.  1 = every warp of the block draws 32-item chunks from one cursor (the
  *       statistics range joins after it has sent its moments); 0 = a fixed share goes to the

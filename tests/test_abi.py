@@ -34,12 +34,15 @@ def test_tuning_table():
     for name in list(_lib.DL_SOLO) + list(_lib.DL_PAIRS) + list(_lib.CRYPTO_SOLO) + list(_lib.CRYPTO_PAIRS):
         v = _lib.tune_variants(name)
         assert len(v) >= 5
+        assert _lib.tune_default(name) in v                            # the compiled default is one of them
         for d in v:
-            t1, t2, mb = (int(x) for x in d.split(":"))
+            t1, t2, mb = (int(x) for x in d.removesuffix(" queue").split(":"))   # "T:0:mb queue": work-queue form of a search
             assert t1 % 32 == 0 and t2 % 32 == 0 and mb >= 1        # whole warps; the DL lists move in 128-thread steps
             if name in _lib.DL_SOLO or name in _lib.DL_PAIRS:
                 assert t1 % 128 == 0 and t2 % 128 == 0              # like the reference's sweep
     assert _lib.lib().hfuse_tune_set(b"no_such_pair", 0, 0) == -7
+    assert _lib.lib().hfuse_tune_default(b"no_such_pair") == -7
+    assert _lib.tune_default("upsample_bnstats_allreduce") in _lib.tune_variants("upsample_bnstats_allreduce")
     assert _lib.lib().hfuse_tune_set(b"im2col_maxpool", 999, 0) < 0
     _lib.tune_set("im2col_maxpool", 1, 2)
     _lib.tune_set("im2col_maxpool", -1, 0)
@@ -94,6 +97,8 @@ def test_fused_search_needs_two_different_hit_records_and_a_count_that_fits_the_
     assert L.hfuse_tune_option(b"im2col_store_path", -1) == 0        # back to the compiled choice per kernel / pair
     assert L.hfuse_tune_option(b"exchange_pair_pool", 1) == 0
     assert L.hfuse_tune_option(b"exchange_pair_pool", -1) == 0
+    assert L.hfuse_tune_option(b"bnstats_load_path", 1) == 0
+    assert L.hfuse_tune_option(b"bnstats_load_path", -1) == 0
 
 
 def test_ops_refuse_cpu_tensors():

@@ -119,6 +119,27 @@ def test_fused_pairs_equal_standalone_for_every_variant(dev, kat, small_dag, pai
         _lib.tune_set(pair, -1, 0)
 
 
+def test_standalone_searches_give_the_same_hits_in_every_block_shape_and_form(dev, kat, small_dag):
+    """Grid-stride and work-queue forms of the four searches, every compiled block shape; a record
+    whose cursor was left non-zero by an earlier call must not matter."""
+    easy = bytes.fromhex(kat["easy_target"])
+    for key in sorted(_lib.CRYPTO_SOLO):
+        want = crypto.run(_mk(key, kat, small_dag[1], easy)).result()
+        assert want[0] > 0
+        descr = _lib.tune_variants(key)
+        assert any(d.endswith(" queue") for d in descr)
+        try:
+            for v in range(len(descr)):
+                _lib.tune_set(key, v, 0)
+                s = _mk(key, kat, small_dag[1], easy)
+                crypto.run(s)
+                assert s.result() == want, (key, descr[v])
+                crypto.run(s)                      # the same record again
+                assert s.result() == want, (key, descr[v], "second run")
+        finally:
+            _lib.tune_set(key, -1, 0)
+
+
 def test_standalone_results_match_oracle_sweeps(dev, kat, small_dag):
     easy = bytes.fromhex(kat["easy_target"])
     hdr, hh = bytes.fromhex(kat["header80"]), bytes.fromhex(kat["header_hash32"])

@@ -270,6 +270,63 @@ def test_im2col_through_shared_memory_and_bulk_stores_gives_the_same_bytes(dev):
         _lib.tune_option("no_such_option", 1)
 
 
+def test_bnstats_through_bulk_loads_into_shared_memory(dev):
+    """The alternative load path (option bnstats_load_path = 1): channels whose image rows are 1 to
+    25 KB long come into shared memory through bulk copies counted on an mbarrier; every block
+    shape, alone and beside another role; shapes outside that range keep the register path."""
+    g = torch.Generator().manual_seed(23)
+    cases = [(32, 20, 28, 28),       # the benchmark's rows (3,136 B), four equal buffer fills
+             (5, 3, 16, 16),         # a single, short fill per channel (1,024 B rows)
+             (19, 7, 20, 20),        # ragged last fill
+             (3, 700, 16, 20),       # more channels than blocks: several units per block
+             (2, 4, 80, 80),         # 25,600 B rows: one row per buffer
+             (4, 5, 81, 80),         # rows too long: register path
+             (6, 9, 6, 6)]           # rows too short: register path
+    try:
+        for path in (1, 0):
+            _lib.tune_option("bnstats_load_path", path)
+            for shape in cases:
+                x = (0.5 + 2.0 * torch.randn(*shape, generator=g))
+                mr, sr = dl.bnstats_f64(x, 1e-5)
+                xd = x.to(dev)
+                for v in range(len(_lib.tune_variants("bnstats"))):
+                    _lib.tune_set("bnstats", v, 0)
+                    op = ops.BnStats(xd, 1e-5, want_moments=True)
+                    ops.run(op)
+                    mean, invstd = op.result()
+                    np.testing.assert_allclose(mean.cpu().double().numpy(), mr.numpy(), rtol=1e-5, atol=1e-6, err_msg=str((path, shape, v)))
+                    np.testing.assert_allclose(invstd.cpu().double().numpy(), sr.numpy(), rtol=1e-5, err_msg=str((path, shape, v)))
+                    m2, s2 = ops.bn_finalize(op.moments, 1e-5)
+                    np.testing.assert_allclose(m2.cpu().double().numpy(), mr.numpy(), rtol=1e-5, atol=1e-6)
+                    np.testing.assert_allclose(s2.cpu().double().numpy(), sr.numpy(), rtol=1e-5)
+                _lib.tune_set("bnstats", -1, 0)
+            # beside another role in the block, every split (the partner's shared memory lies in front)
+            x = (0.5 + 2.0 * torch.randn(8, 40, 28, 28, generator=g))
+            mr, sr = dl.bnstats_f64(x, 1e-5)
+            up_in = torch.rand(2, 6, 12, 16, generator=g)
+            want_up = dl.upsample_numpy(up_in.numpy(), 24, 32, False)
+            hv = torch.randn(50000, generator=g)
+            want_h = torch.histc(hv, 256, -4.0, 4.0)
+            for name, mk in (("upsample_bnstats", lambda: ops.Upsample(up_in.to(dev), scale_factor=2)),
+                             ("histc_bnstats", lambda: ops.Histc(hv.to(dev), 256, -4.0, 4.0))):
+                for v in range(len(_lib.tune_variants(name))):
+                    _lib.tune_set(name, v, 0)
+                    a, b = mk(), ops.BnStats(x.to(dev), 1e-5)
+                    ops.run_pair(a, b)
+                    mean, invstd = b.result()
+                    np.testing.assert_allclose(mean.cpu().double().numpy(), mr.numpy(), rtol=1e-5, atol=1e-6, err_msg=str((path, name, v)))
+                    np.testing.assert_allclose(invstd.cpu().double().numpy(), sr.numpy(), rtol=1e-5, err_msg=str((path, name, v)))
+                    if name == "upsample_bnstats":
+                        assert np.array_equal(a.out.cpu().numpy(), want_up), (path, v)
+                    else:
+                        assert torch.equal(a.result().cpu().float(), want_h), (path, v)
+                _lib.tune_set(name, -1, 0)
+    finally:
+        _lib.tune_option("bnstats_load_path", -1)
+        for name in ("bnstats", "upsample_bnstats", "histc_bnstats"):
+            _lib.tune_set(name, -1, 0)
+
+
 def test_error_codes_on_device_buffers(dev):
     x = torch.zeros(1, 1, 4, 4, device=dev)
     with pytest.raises(ValueError):

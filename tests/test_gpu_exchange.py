@@ -74,25 +74,32 @@ def test_statistics_range_takes_over_any_share_of_the_upsample(dev):
         _lib.tune_set("upsample_bnstats_allreduce", -1, 0)
         _lib.tune_set_share("upsample_bnstats_allreduce", -1)
         ex.close()
-    # the cursor form: every warp of either range draws chunks of the upsample; same bits for every split
+    # the cursor form: every warp of either range draws chunks of the upsample; same bits for every split.
+    # Statistics input with rows long enough for the bulk-load path too, read both ways.
+    x_long = 0.5 + 2.0 * torch.randn(5, 40, 16, 20, generator=g)
+    stats_inputs = [(x, mr, sr, (0,)), (x_long, *dl.bnstats_f64(x_long, 1e-5), (0, 1))]
     ex = BnExchange(40)
     try:
         _lib.tune_option("exchange_pair_pool", 1)
         for variant in range(len(_lib.tune_variants("upsample_bnstats_allreduce"))):
             _lib.tune_set("upsample_bnstats_allreduce", variant, 0)
-            for shape, kw in cases:
-                up = torch.rand(*shape, generator=g)
-                a, b = ops.Upsample(up.to(dev), **kw), ops.BnStats(x.to(dev), 1e-5)
-                a.out.fill_(float("nan"))
-                ex.run_pair(a, b)
-                oh, ow = a.out.shape[-2:]
-                assert np.array_equal(a.out.cpu().numpy(), dl.upsample_numpy(up.numpy(), oh, ow)), (variant, shape)
-                np.testing.assert_allclose(b.mean.cpu().double().numpy(), mr.numpy(), rtol=1e-5)
-                np.testing.assert_allclose(b.invstd.cpu().double().numpy(), sr.numpy(), rtol=1e-5)
+            for xs, mrs, srs, paths in stats_inputs:
+                for path in paths:
+                    _lib.tune_option("bnstats_load_path", path)
+                    for shape, kw in cases:
+                        up = torch.rand(*shape, generator=g)
+                        a, b = ops.Upsample(up.to(dev), **kw), ops.BnStats(xs.to(dev), 1e-5)
+                        a.out.fill_(float("nan"))
+                        ex.run_pair(a, b)
+                        oh, ow = a.out.shape[-2:]
+                        assert np.array_equal(a.out.cpu().numpy(), dl.upsample_numpy(up.numpy(), oh, ow)), (variant, shape, path)
+                        np.testing.assert_allclose(b.mean.cpu().double().numpy(), mrs.numpy(), rtol=1e-5, atol=1e-6)
+                        np.testing.assert_allclose(b.invstd.cpu().double().numpy(), srs.numpy(), rtol=1e-5)
         assert not ex.timed_out()
     finally:
         _lib.tune_set("upsample_bnstats_allreduce", -1, 0)
         _lib.tune_option("exchange_pair_pool", -1)
+        _lib.tune_option("bnstats_load_path", -1)
         ex.close()
     with pytest.raises(_lib.HfuseError):
         _lib.tune_set_share("upsample_bnstats", 100)          # only the exchange pair has a share
