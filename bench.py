@@ -947,20 +947,21 @@ def run_tune_share(args, torch, _lib, ex, sets, nsets, dev, rank, barrier, use_d
     name = "upsample_bnstats_allreduce"
     descr = _lib.tune_variants(name)
     variants = [v for v, d in enumerate(descr) if ":0:" not in d]
-    # "pool": items drawn from a cursor by both ranges; "pool_bulk": the same with the statistics read through bulk copies
-    shares = (0, 100, 200, 300, 400, 500, "pool", "pool_bulk")
+    # "pool": items drawn from a cursor by both ranges; "pool_bulk": the same with the statistics read through bulk
+    # copies; "0_bulk": no share (the upsample stays with its own range), statistics through bulk copies
+    shares = (0, 100, 200, 300, 400, 500, "pool", "pool_bulk", "0_bulk")
     reps, gsteps = 6, 4 * nsets
     table = {}
     for v in variants:
         row = {}
         for share in shares:
             _lib.tune_set(name, v, 0)
-            _lib.tune_option("bnstats_load_path", 1 if share == "pool_bulk" else 0)
+            _lib.tune_option("bnstats_load_path", 1 if str(share).endswith("_bulk") else 0)
             if share in ("pool", "pool_bulk"):
                 _lib.tune_set_share(name, -1)
                 _lib.tune_option("exchange_pair_pool", 1)
             else:
-                _lib.tune_set_share(name, share)
+                _lib.tune_set_share(name, 0 if share == "0_bulk" else share)
             for i in range(nsets):
                 ex.run_pair(*sets[i])
             torch.cuda.synchronize()
@@ -993,8 +994,8 @@ def run_tune_share(args, torch, _lib, ex, sets, nsets, dev, rank, barrier, use_d
         best = min(((t, d, sh) for d, row in table.items() for sh, t in row.items()))
         print(json.dumps({"pair": name, "n_gpus": args.gpus, "unit": "us per step, max over ranks",
                           "best": {"variant": best[1], "index": descr.index(best[1]),
-                                   "share_permille": -1 if best[2].startswith("pool") else int(best[2]),
-                                   "pool": best[2].startswith("pool"), "bnstats_bulk": int(best[2] == "pool_bulk"),
+                                   "share_permille": -1 if best[2].startswith("pool") else int(best[2].split("_")[0]),
+                                   "pool": best[2].startswith("pool"), "bnstats_bulk": int(best[2].endswith("_bulk")),
                                    "us": best[0]},
                           "exchange_timed_out": timed_out, "table": table}))
     if use_dist:

@@ -62,8 +62,10 @@ def apply_share(path: str, csrc: str = CSRC) -> None:
                  ("kDefaultPoolPair_upsample_bnstats_allreduce", res["best"]["index"]),
                  ("kBnStatsBulk_upsample_bnstats_allreduce", res["best"].get("bnstats_bulk", 0)))
     else:
-        pairs = ((f"kDefaultPair_upsample_bnstats_allreduce{suffix}", res["best"]["index"]),
-                 (f"kDefaultShare_upsample_bnstats_allreduce{suffix}", res["best"]["share_permille"]))
+        pairs = (("kDefaultPool_upsample_bnstats_allreduce", 0),
+                 (f"kDefaultPair_upsample_bnstats_allreduce{suffix}", res["best"]["index"]),
+                 (f"kDefaultShare_upsample_bnstats_allreduce{suffix}", res["best"]["share_permille"]),
+                 ("kBnStatsBulk_upsample_bnstats_allreduce", res["best"].get("bnstats_bulk", 0)))
     for key, val in pairs:
         src, n = re.subn(rf"({key} = )\d+;", rf"\g<1>{int(val)};", src)
         assert n == 1, key

@@ -1178,43 +1178,51 @@ struct BnStatsRole {
             fence_mbar_init();
         }
         role_sync<BAR, T>();
-        unsigned used = 0;            // buffer fills consumed so far; every thread counts alike
+        // The fills of all of this block's channels form one sequence: fill g belongs to channel
+        // block + (g / nfill) * nblocks and holds its rows [(g % nfill) * R, ...); it goes to buffer
+        // g % NB.  NB fills are in flight ahead of the reader, across channel boundaries too, so the
+        // second channel of a block does not start with an empty ring.
+        const unsigned blk = (unsigned)ctx.block, nblk = (unsigned)ctx.nblocks;
+        const unsigned nunits = blk < (unsigned)a.C ? ((unsigned)a.C - blk + nblk - 1u) / nblk : 0u;
+        const unsigned total = nunits * nfill;
+        auto issue = [&](unsigned g) {
+            const unsigned u = blk + (g / nfill) * nblk, k = g % nfill;
+            const unsigned n = min(R, rows - k * R), slot = g % NB;
+            const float* src = a.x + (size_t)u * a.HW + (size_t)(k * R) * img_stride;
+            mbar_expect_tx(full + slot, n * row_bytes);
+            unsigned char* dst = tiles + (size_t)slot * buf_bytes;
+            for (unsigned r = 0; r < n; ++r)
+                bulk_load(dst + (size_t)r * row_bytes, src + (size_t)r * img_stride, row_bytes, full + slot);
+        };
+        if (ctx.tid == 0)
+            for (unsigned g = 0; g < NB && g < total; ++g) issue(g);
         int parity = 0;
         bool ok = true;
-        for (unsigned u = ctx.block; u < (unsigned)a.C; u += ctx.nblocks, parity ^= 1) {
-            const float* xc = a.x + (size_t)u * a.HW;
-            auto issue = [&](unsigned k, unsigned f) {      // rows [k*R, k*R + n) of channel u as fill number f
-                const unsigned n = min(R, rows - k * R), slot = f % NB;
-                mbar_expect_tx(full + slot, n * row_bytes);
-                unsigned char* dst = tiles + (size_t)slot * buf_bytes;
-                for (unsigned r = 0; r < n; ++r)
-                    bulk_load(dst + (size_t)r * row_bytes, xc + (size_t)(k * R + r) * img_stride, row_bytes, full + slot);
-            };
-            // every thread is past its last read of all buffers (the previous unit ended with the role's barrier)
-            if (ctx.tid == 0)
-                for (unsigned k = 0; k < NB && k < nfill; ++k) issue(k, used + k);
-            float cnt = 0.f, sum = 0.f, sq = 0.f, shift = 0.f;
-            for (unsigned k = 0; k < nfill; ++k, ++used) {
-                const unsigned slot = used % NB, par = (used / NB) & 1u;
-                ok &= mbar_wait(full + slot, par, kTimeoutNs);
-                const unsigned items = min(R, rows - k * R) * row4;
-                const float4* t = reinterpret_cast<const float4*>(tiles + (size_t)slot * buf_bytes);
-                for (unsigned i = ctx.tid; i < items; i += T) {
-                    const float4 v = t[i];
-                    if (cnt == 0.f) shift = v.x;
-                    const float d0 = v.x - shift, d1 = v.y - shift, d2 = v.z - shift, d3 = v.w - shift;
-                    sum += (d0 + d1) + (d2 + d3);
-                    sq = fmaf(d0, d0, fmaf(d1, d1, fmaf(d2, d2, fmaf(d3, d3, sq))));
-                    cnt += 4.f;
-                }
-                if (k + NB < nfill) {
-                    role_sync<BAR, T>();
-                    if (ctx.tid == 0) issue(k + NB, used + NB);
-                }
+        float cnt = 0.f, sum = 0.f, sq = 0.f, shift = 0.f;
+        for (unsigned g = 0; g < total; ++g) {
+            const unsigned slot = g % NB, k = g % nfill;
+            ok &= mbar_wait(full + slot, (g / NB) & 1u, kTimeoutNs);
+            const unsigned items = min(R, rows - k * R) * row4;
+            const float4* t = reinterpret_cast<const float4*>(tiles + (size_t)slot * buf_bytes);
+            for (unsigned i = ctx.tid; i < items; i += T) {
+                const float4 v = t[i];
+                if (cnt == 0.f) shift = v.x;
+                const float d0 = v.x - shift, d1 = v.y - shift, d2 = v.z - shift, d3 = v.w - shift;
+                sum += (d0 + d1) + (d2 + d3);
+                sq = fmaf(d0, d0, fmaf(d1, d1, fmaf(d2, d2, fmaf(d3, d3, sq))));
+                cnt += 4.f;
             }
-            // a wait that ran out of time: the statistics of this channel come out as NaN
-            if (!__all_sync(0xffffffffu, ok)) sum = __int_as_float(0x7fc00000);
-            fold_unit<T, BAR, XCHG, DEFER>(a, ctx, word, parity, u, 0u, cnt, sum, sq, shift);
+            if (g + NB < total) {          // the buffer is refilled once every thread has read it
+                role_sync<BAR, T>();
+                if (ctx.tid == 0) issue(g + NB);
+            }
+            if (k + 1u == nfill) {         // the channel is complete
+                // a wait that ran out of time: the statistics of this channel come out as NaN
+                if (!__all_sync(0xffffffffu, ok)) sum = __int_as_float(0x7fc00000);
+                fold_unit<T, BAR, XCHG, DEFER>(a, ctx, word, parity, blk + (g / nfill) * nblk, 0u, cnt, sum, sq, shift);
+                parity ^= 1;
+                cnt = 0.f; sum = 0.f; sq = 0.f; shift = 0.f;
+            }
         }
         // thread 0 is past the last fold's barrier, so nobody waits on the barriers any more: give
         // their shared memory back (a vertically fused partner reuses it)

@@ -251,8 +251,8 @@ HFUSE_API int hfuse_upsample_bnstats_allreduce_f32(HFUSE_UPSAMPLE_PARAMS(a_), HF
  * absent ethminer sources).  Device memory; reset it before every search (hfuse_hits_reset):
  * `count` must start at zero and counts every hit found even beyond HFUSE_MAX_HITS; slots
  * are filled in arrival order, so sort by nonce before comparing.  `reserved` is the work
- * queue cursor of the fused searches (thread ranges take chunks of nonces from it); the
- * fused entry points clear it themselves.  The two halves of a fused search need two DIFFERENT
+ * queue cursor of the fused searches and of the work-queue form of the standalone ones (warps
+ * take chunks of nonces from it); the entry points clear it themselves.  The two halves of a fused search need two DIFFERENT
  * records (one record for both returns HFUSE_ERR_BAD_ARG).  count <= 2^61 (2^32 for the 32-bit
  * nonces). */
 typedef struct hfuse_hits {
@@ -273,6 +273,9 @@ HFUSE_API int hfuse_hits_reset(hfuse_hits* hits, hfuse_stream_t stream);
     const void *P##dag, uint32_t P##dag_items, const uint8_t *P##header_hash32, uint64_t P##start, \
         uint64_t P##count, const uint8_t *P##target32, hfuse_hits *P##hits
 
+/* Standalone searches.  Every search is compiled as a grid-stride sweep and as a work queue
+ * (variants "T:0:minBlocks" and "T:0:minBlocks queue" of hfuse_tune_describe); the compiled default
+ * is whichever the sweep on B200 found faster (ethash: the queue, 676 vs 581 MH/s over 2^30 nonces). */
 HFUSE_API int hfuse_blake256_search(HFUSE_BLAKE256_PARAMS(), hfuse_stream_t stream);
 HFUSE_API int hfuse_sha256d_search(HFUSE_SHA256D_PARAMS(), hfuse_stream_t stream);
 HFUSE_API int hfuse_sia_blake2b_search(HFUSE_SIA_PARAMS(), hfuse_stream_t stream);
