@@ -473,6 +473,7 @@ def check_headline(torch, sets, w, ex, dev, world):
 NCU_TRAFFIC_BYTES = {"fused_kernel<UpsampleRole,BnStatsRole,896,128,1>": 98_881_792,
                      "fused_kernel<UpsampleRole,BnStatsRole,512,256,2>": 101_843_456,
                      "fused_pool_kernel<UpsampleRole,BnStatsXchgRole,896,128,1>": 98_200_000,
+                     "fused_pool_kernel<UpsampleRole,BnStatsXchgRole,384,128,2>": None,
                      "fused_pool_kernel<UpsampleRole,BnStatsXchgRole,512,256,2>": 101_500_000,
                      "fused_pool_kernel<UpsampleRole,BnStatsXchgRole,384,256,2>": 100_000_000}
 
@@ -499,6 +500,8 @@ def run_ours(args):
 
     if args.im2col_path != "default":
         _lib.tune_option("im2col_store_path", 1 if args.im2col_path == "bulk" else 0)
+    if args.histc_path != "default":
+        _lib.tune_option("histc_load_path", 1 if args.histc_path == "bulk" else 0)
     if args.bnstats_path != "default":
         _lib.tune_option("bnstats_load_path", 1 if args.bnstats_path == "bulk" else 0)
     if args.only:
@@ -535,7 +538,8 @@ def run_ours(args):
         _lib.tune_set("upsample_bnstats_allreduce" if ex is not None else "upsample_bnstats", args.pair_variant, 0)
 
     def shape_of(pair):      # "T1,T2,minBlocks" of the variant that will run
-        d = _lib.tune_variants(pair)[args.pair_variant] if args.pair_variant >= 0 else _lib.tune_default(pair)
+        wide = "_wide" if pair.endswith("_allreduce") and world > 4 else ""      # the exchange pair's default beyond four ranks
+        d = _lib.tune_variants(pair)[args.pair_variant] if args.pair_variant >= 0 else _lib.tune_default(pair + wide)
         return d.replace(":", ",")
     if args.share_permille >= 0 and ex is not None:
         _lib.tune_set_share("upsample_bnstats_allreduce", args.share_permille)
@@ -1165,11 +1169,12 @@ def run_tune(args, torch, ops, crypto, workloads, dev):
         for this kernel or pair; None where the kernel has no such role."""
         ips = (0, 1) if "im2col" in name else (None,)
         bps = (0, 1) if "bnstats" in name else (None,)
-        return [(ip, bp) for ip in ips for bp in bps]
+        hps = (0, 1) if "histc" in name else (None,)
+        return [(ip, bp, hp) for ip in ips for bp in bps for hp in hps]
 
     def label(d, path):
-        ip, bp = path
-        return d + ("" if ip is None else f" path{ip}") + ("" if bp is None else f" bn{bp}")
+        ip, bp, hp = path
+        return d + ("" if ip is None else f" path{ip}") + ("" if bp is None else f" bn{bp}") + ("" if hp is None else f" h{hp}")
 
     def sweep(name, run_one):
         """{((im2col path, statistics path), variant description): us} over every path and compiled variant."""
@@ -1180,12 +1185,15 @@ def run_tune(args, torch, ops, crypto, workloads, dev):
                     _lib.tune_option("im2col_store_path", path[0])
                 if path[1] is not None:
                     _lib.tune_option("bnstats_load_path", path[1])
+                if path[2] is not None:
+                    _lib.tune_option("histc_load_path", path[2])
                 for v, d in enumerate(_lib.tune_variants(name)):
                     _lib.tune_set(name, v, 0)
                     times[(path, d)] = round(graph_region(torch, run_one, NS, steps, 3) * 1e3, 2)
         finally:
             _lib.tune_option("im2col_store_path", -1)
             _lib.tune_option("bnstats_load_path", -1)
+            _lib.tune_option("histc_load_path", -1)
             _lib.tune_set(name, -1, 0)
         return times
 
@@ -1199,6 +1207,8 @@ def run_tune(args, torch, ops, crypto, workloads, dev):
             out["im2col_bulk"] = path[0]
         if path[1] is not None:
             out["bnstats_bulk"] = path[1]
+        if path[2] is not None:
+            out["histc_bulk"] = path[2]
         return out, path
 
     for key in _lib.DL_SOLO:
@@ -1213,6 +1223,8 @@ def run_tune(args, torch, ops, crypto, workloads, dev):
             solo_im2col_path = path[0]
         if path[1] is not None:
             solo_bn_path = path[1]
+        if path[2] is not None:
+            solo_histc_path = path[2]
         del sets
         torch.cuda.empty_cache()
     for name, (ka, kb) in _lib.DL_PAIRS.items():
@@ -1222,6 +1234,8 @@ def run_tune(args, torch, ops, crypto, workloads, dev):
             _lib.tune_option("im2col_store_path", solo_im2col_path)
         if "bnstats" in name:                    # and so does the standalone statistics kernel
             _lib.tune_option("bnstats_load_path", solo_bn_path)
+        if "histc" in name:                      # and the standalone histogram kernel
+            _lib.tune_option("histc_load_path", solo_histc_path)
         t_b2b = graph_region(torch, lambda i: ops.run_back_to_back(*sets[i % NS]), NS, steps, 3) * 1e3
         times = sweep(name, lambda i: ops.run_pair(*sets[i % NS]))
         out, _ = describe(times, name, True)
@@ -1365,6 +1379,8 @@ def main():
     ap.add_argument("--im2col-path", default="default", choices=["default", "registers", "bulk"],
                     help="store path of the im2col role: the compiled choice per kernel / pair, register tiles + "
                          "streaming stores, or shared-memory tile + bulk (TMA) stores")
+    ap.add_argument("--histc-path", default="default", choices=["default", "registers", "bulk"],
+                    help="load path of the histogram role: the compiled choice per kernel / pair, 16-byte loads into registers, or bulk (TMA) copies into a shared-memory ring")
     ap.add_argument("--bnstats-path", default="default", choices=["default", "registers", "bulk"],
                     help="load path of the statistics role: the compiled choice per kernel / pair, 16-byte loads into registers, or bulk (TMA) copies into shared memory")
     ap.add_argument("--pair-variant", type=int, default=-1,

@@ -188,7 +188,7 @@ def tune_default(name: str) -> str:
     """Descriptor ("T1:T2:minBlocks") of the compiled default variant of a kernel or pair."""
     v = lib().hfuse_tune_default(name.encode())
     check(min(v, 0), f"tune_default({name})")
-    return tune_variants(name)[v]
+    return tune_variants(name.removesuffix("_wide"))[v]      # "<exchange pair>_wide": its default beyond four ranks
 
 
 def tune_variants(name: str) -> list[str]:

@@ -41,6 +41,9 @@ def apply(path: str, csrc: str = CSRC) -> None:
                 if "im2col_bulk" in entry:       # store path of the im2col role in this kernel / pair
                     src, n = re.subn(rf"(kIm2colBulk_{name} = )\d+;", rf"\g<1>{int(entry['im2col_bulk'])};", src)
                     assert n == 1, name
+                if "histc_bulk" in entry:        # load path of the histogram role in this kernel / pair
+                    src, n = re.subn(rf"(kHistcBulk_{name} = )\d+;", rf"\g<1>{int(entry['histc_bulk'])};", src)
+                    assert n == 1, name
                 if "bnstats_bulk" in entry:      # load path of the statistics role in this kernel / pair
                     src, n = re.subn(rf"(kBnStatsBulk_{name} = )\d+;", rf"\g<1>{int(entry['bnstats_bulk'])};", src)
                     assert n == 1, name
@@ -57,9 +60,10 @@ def apply_share(path: str, csrc: str = CSRC) -> None:
     suffix = "_wide" if int(res["n_gpus"]) > 2 else ""
     p = os.path.join(csrc, "dl_tuned.inc")
     src = open(p).read()
-    if res["best"].get("pool"):       # the cursor form won: one thread split for any number of ranks
+    if res["best"].get("pool"):       # the cursor form won: one thread split up to four ranks, one beyond
+        wide = "_wide" if int(res["n_gpus"]) > 4 else ""
         pairs = (("kDefaultPool_upsample_bnstats_allreduce", 1),
-                 ("kDefaultPoolPair_upsample_bnstats_allreduce", res["best"]["index"]),
+                 (f"kDefaultPoolPair_upsample_bnstats_allreduce{wide}", res["best"]["index"]),
                  ("kBnStatsBulk_upsample_bnstats_allreduce", res["best"].get("bnstats_bulk", 0)))
     else:
         pairs = (("kDefaultPool_upsample_bnstats_allreduce", 0),

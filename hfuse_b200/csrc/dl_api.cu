@@ -83,6 +83,9 @@ int dl_default_variant(const char* name) {
     if (!strcmp(name, "upsample_bnstats_allreduce"))
         return kDefaultPool_upsample_bnstats_allreduce == 1 ? kDefaultPoolPair_upsample_bnstats_allreduce
                                                             : kDefaultPair_upsample_bnstats_allreduce;
+    if (!strcmp(name, "upsample_bnstats_allreduce_wide"))      // what the exchange pair runs with more than four ranks
+        return kDefaultPool_upsample_bnstats_allreduce == 1 ? kDefaultPoolPair_upsample_bnstats_allreduce_wide
+                                                            : kDefaultPair_upsample_bnstats_allreduce_wide;
     return HFUSE_ERR_UNKNOWN_PAIR;
 }
 }  // namespace hfuse

@@ -162,9 +162,11 @@ int hfuse_upsample_bnstats_allreduce_f32(HFUSE_UPSAMPLE_PARAMS(a_), HFUSE_BNSTAT
     const Tune t = tune_get("upsample_bnstats_allreduce");
     const int opt = option_get("exchange_pair_pool", -1);
     const bool pool = t.share_permille < 0 && (opt >= 0 ? opt == 1 : kDefaultPool_upsample_bnstats_allreduce == 1);
-    if (pool)
-        return dispatch_pair_pool<UpsampleRole, BnStatsXchgRole>("upsample_bnstats_allreduce",
-                                                                 kDefaultPoolPair_upsample_bnstats_allreduce, a, b, S_(stream));
+    if (pool)      // thread split measured at 1, 2, 4 and at 8 ranks (bench.py --tune-share)
+        return dispatch_pair_pool<UpsampleRole, BnStatsXchgRole>(
+            "upsample_bnstats_allreduce",
+            ex->world > 4 ? kDefaultPoolPair_upsample_bnstats_allreduce_wide : kDefaultPoolPair_upsample_bnstats_allreduce, a,
+            b, S_(stream));
     const bool wide = ex->world > 2;      // measured at 2 and at 8 ranks (bench.py --tune-share)
     return dispatch_pair_share<UpsampleRole, BnStatsXchgRole>(
         "upsample_bnstats_allreduce",

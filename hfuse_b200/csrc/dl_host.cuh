@@ -105,7 +105,6 @@ int prep_bnstats(HFUSE_BNSTATS_PARAMS(), BnStatsArgs& a) {
     a.vec = (HW % 4) == 0;
     a.ws = workspace; a.ws_bytes = workspace_bytes;
     a.xchg = BnXchg{};
-    // bulk-load path: rows of 1 to 25 KB that are 16-byte multiples; as few, equally long buffer fills as fit 25 KB
     // bulk-load path: rows of 1 to 25 KB that are 16-byte multiples; three buffers, each holding as many rows
     // as fit 25 KB, all fills of a channel equally long (measured on B200: two to four buffers of 12.5 or 25 KB
     // are within 0.3 us of each other; alone or with a large statistics range the register path is faster)
@@ -163,6 +162,9 @@ int prep_histc(HFUSE_HISTC_PARAMS(), HistcArgs& a) {
     a.inv_range = a.range_pow2 ? 1.f / a.range : 0.f;
     a.copies = 0;
     a.lane_private = 0;
+    // bulk-load sweep: the [bin][lane] histogram (up to 256 bins) and fewer than 2^31 16-byte items
+    a.bulk = 0;
+    a.bulk_ok = (a.fast && nbins <= 256 && x) ? 1 : 0;
     return HFUSE_OK;
 }
 
@@ -193,6 +195,13 @@ void choose_path(BnStatsArgs& a, const char* name) {
     if (!a.bulk_ok) return;
     const int opt = option_get("bnstats_load_path", -1);
     a.bulk = (opt >= 0 ? opt == 1 : default_bnstats_bulk(name) == 1) ? 1 : 0;
+}
+// And for the histogram role's load path (option "histc_load_path").
+int default_histc_bulk(const char* name);
+void choose_path(HistcArgs& a, const char* name) {
+    if (!a.bulk_ok) return;
+    const int opt = option_get("histc_load_path", -1);
+    a.bulk = (opt >= 0 ? opt == 1 : default_histc_bulk(name) == 1) ? 1 : 0;
 }
 template <class A> void choose_path(A&, const char*) {}
 
@@ -344,6 +353,15 @@ int default_bnstats_bulk(const char* name) {
     if (!strcmp(name, "upsample_bnstats")) return kBnStatsBulk_upsample_bnstats;
     if (!strcmp(name, "histc_bnstats")) return kBnStatsBulk_histc_bnstats;
     if (!strcmp(name, "upsample_bnstats_allreduce")) return kBnStatsBulk_upsample_bnstats_allreduce;
+    return 0;
+}
+
+int default_histc_bulk(const char* name) {
+    if (!strcmp(name, "histc")) return kHistcBulk_histc;
+    if (!strcmp(name, "im2col_histc")) return kHistcBulk_im2col_histc;
+    if (!strcmp(name, "histc_maxpool")) return kHistcBulk_histc_maxpool;
+    if (!strcmp(name, "histc_upsample")) return kHistcBulk_histc_upsample;
+    if (!strcmp(name, "histc_bnstats")) return kHistcBulk_histc_bnstats;
     return 0;
 }
 

@@ -628,12 +628,19 @@ struct HistcArgs {
     int copies;         // private shared-memory histograms per role (0 = global atomics only)
     int lane_private;   // shared histogram laid out [bin][32 lanes]: lane l only ever touches bank l
     int fast;           // fewer than 2^31 16-byte items: 32-bit indices and the peeled loop
+    int bulk_ok;        // the shape allows the bulk-load sweep (the host picks per kernel or pair)
+    int bulk;           // 1: the values come through bulk (TMA) copies into a shared-memory ring (sweep_bulk)
 };
 
 struct HistcRole {
     using Args = HistcArgs;
-    static int smem_bytes(const Args& a, int) {
-        return (a.lane_private ? 32 : a.copies) * a.nbins * (int)sizeof(unsigned);
+    // bulk-load sweep: a ring of kBulkBufs buffers of kBulkU 16-byte items per thread behind the histogram,
+    // with a "full" and an "empty" mbarrier per buffer in front of it
+    static constexpr int kBulkU = 2, kBulkBufs = 4;
+    static __host__ __device__ __forceinline__ int bulk_chunk_bytes(int T) { return T * kBulkU * 16; }
+    static int smem_bytes(const Args& a, int T) {
+        return (a.lane_private ? 32 : a.copies) * a.nbins * (int)sizeof(unsigned) +
+               (a.bulk ? 64 + kBulkBufs * bulk_chunk_bytes(T) : 0);
     }
     // Up to 256 bins: one counter per (bin, lane) = 32 KB at most.  Lane l of every warp
     // only touches word bin*32 + l, i.e. bank l, so a warp's 32 increments never meet in a
@@ -647,6 +654,7 @@ struct HistcRole {
             return 0;
         }
         a.lane_private = 0;
+        a.bulk = 0;          // the ring sits behind the [bin][lane] histogram only
         const int budget = 16 * 1024;
         int copies = budget / (a.nbins * (int)sizeof(unsigned));
         if (copies > T / 32) copies = T / 32;
@@ -722,6 +730,75 @@ struct HistcRole {
         for (; i < n4; i += stride) count4(ldg_stream4(a.x + 4ull * i));     // ragged end: fewer than U items per thread
         if (ctx.block == 0)      // n % 4 values
             for (long long j = 4ll * n4 + ctx.tid; j < a.n; j += T) count<SHIFT, POW2>(a, __ldg(a.x + j), sbase, last);
+    }
+
+    // Bulk-load sweep ([bin][lane] histogram, fewer than 2^31 items).  The input is cut into chunks of
+    // T * kBulkU 16-byte items; block b takes chunks b, b + blocks, ...  Thread 0 brings a chunk into
+    // the ring with ONE bulk (TMA) copy that signals the buffer's "full" mbarrier with its bytes; every
+    // warp waits for "full", reads its items (thread t: items t, t + T, ...: no bank conflicts), says so
+    // on the buffer's "empty" mbarrier (one arrival per warp) and counts; thread 0 refills a buffer once
+    // its "empty" phase is complete, one chunk behind its own reading so that it rarely has to wait.
+    // The loads then cost the sweep no issue slots, no registers and no long-latency stalls: what is
+    // left are shared-memory reads.  The ragged end (fewer items than a chunk) goes through plain loads.
+    // Returns false when a wait ran out of time (the counts are then incomplete).  The mbarriers at the
+    // head of the ring must have been initialised (bulk_init) and a barrier of the role passed since.
+    static __device__ __forceinline__ void bulk_init(unsigned char* ring, int warps) {
+        unsigned long long* full = reinterpret_cast<unsigned long long*>(ring);
+        for (int b = 0; b < kBulkBufs; ++b) { mbar_init(full + b, 1u); mbar_init(full + kBulkBufs + b, (uint32_t)warps); }
+        fence_mbar_init();
+    }
+    static __device__ __forceinline__ void bulk_done(unsigned char* ring) {
+        unsigned long long* full = reinterpret_cast<unsigned long long*>(ring);
+        for (int b = 0; b < 2 * kBulkBufs; ++b) mbar_inval(full + b);
+    }
+    template <int T, int SHIFT, bool POW2>
+    static __device__ __forceinline__ bool sweep_bulk(const Args& a, const RoleCtx& ctx, uint32_t sbase, unsigned char* ring) {
+        constexpr int U = kBulkU, NB = kBulkBufs;
+        constexpr uint32_t CI = (uint32_t)T * U;              // 16-byte items per chunk
+        constexpr unsigned long long kTimeoutNs = 2000000000ull;
+        unsigned long long* full = reinterpret_cast<unsigned long long*>(ring);
+        unsigned long long* empty = full + NB;
+        const float4* tiles = reinterpret_cast<const float4*>(ring + 64);
+        const int last = a.nbins - 1;
+        const uint32_t n4 = (uint32_t)(a.n >> 2);
+        const uint32_t nchunks = n4 / CI, blk = (uint32_t)ctx.block, nblk = (uint32_t)ctx.nblocks;
+        const uint32_t mine = blk < nchunks ? (nchunks - blk + nblk - 1u) / nblk : 0u;
+        const int lane = ctx.tid & 31;
+        auto count4 = [&](const float4& v) {
+            count<SHIFT, POW2>(a, v.x, sbase, last); count<SHIFT, POW2>(a, v.y, sbase, last);
+            count<SHIFT, POW2>(a, v.z, sbase, last); count<SHIFT, POW2>(a, v.w, sbase, last);
+        };
+        auto issue = [&](uint32_t g) {                       // chunk blk + g * nblk as fill number g
+            const uint32_t slot = g % NB;
+            mbar_expect_tx(full + slot, CI * 16u);
+            bulk_load(const_cast<float4*>(tiles) + (size_t)slot * CI, a.x + 4ull * CI * (blk + g * nblk), CI * 16u, full + slot);
+        };
+        if (ctx.tid == 0)
+            for (uint32_t g = 0; g < (uint32_t)NB && g < mine; ++g) issue(g);
+        bool ok = true;
+        for (uint32_t g = 0; g < mine; ++g) {
+            const uint32_t slot = g % NB, par = (g / NB) & 1u;
+            // a wait that ran out of time ends the sweep for the whole warp (the other warps follow within their own limit)
+            ok = __all_sync(0xffffffffu, ok && mbar_wait(full + slot, par, kTimeoutNs));
+            if (!ok) break;
+            float4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) v[u] = tiles[(size_t)slot * CI + (uint32_t)ctx.tid + (uint32_t)u * T];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty + slot);
+            // refill the buffer of the chunk before this one: its readers have had a whole chunk's time
+            if (ctx.tid == 0 && g >= 1u && g - 1u + NB < mine) {
+                if (mbar_wait(empty + (g - 1u) % NB, ((g - 1u) / NB) & 1u, kTimeoutNs)) issue(g - 1u + NB);
+                else ok = false;          // nothing more is issued; every warp's next wait runs out and ends its sweep
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) count4(v[u]);
+        }
+        if (blk == nblk - 1u)      // fewer items than a chunk
+            for (uint32_t i = nchunks * CI + (uint32_t)ctx.tid; i < n4; i += T) count4(ldg_stream4(a.x + 4ull * i));
+        if (ctx.block == 0)        // n % 4 values
+            for (long long j = 4ll * n4 + ctx.tid; j < a.n; j += T) count<SHIFT, POW2>(a, __ldg(a.x + j), sbase, last);
+        return ok;
     }
 
     // General sweep: 64-bit indices, any histogram placement.  SHARED selects the address space at
@@ -803,17 +880,26 @@ struct HistcRole {
         unsigned* sh = reinterpret_cast<unsigned*>(ctx.smem);
         const int words = (a.lane_private ? 32 : a.copies) * a.nbins;
         for (int i = ctx.tid; i < words; i += T) sh[i] = 0u;
+        unsigned char* ring = ctx.smem + words * (int)sizeof(unsigned);      // bulk-load sweep only
+        if (a.bulk && ctx.tid == 0) bulk_init(ring, T / 32);
         role_sync<BAR, T>();
         unsigned* hist = a.lane_private ? sh : sh + ((ctx.tid >> 5) % a.copies) * a.nbins;
+        bool ok = true;
         if (a.fast) {
             const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(hist) + (a.lane_private ? 4u * (ctx.tid & 31) : 0u);
-            if (a.lane_private) sweep_fast_pick<T, 7>(a, ctx, sbase);
+            if (a.bulk) {          // only with the [bin][lane] histogram (plan)
+                if (a.range_pow2) ok = sweep_bulk<T, 7, true>(a, ctx, sbase, ring);
+                else ok = sweep_bulk<T, 7, false>(a, ctx, sbase, ring);
+            } else if (a.lane_private) sweep_fast_pick<T, 7>(a, ctx, sbase);
             else sweep_fast_pick<T, 2>(a, ctx, sbase);
         } else {
             sweep<T, true>(a, ctx, hist);
         }
         role_sync<BAR, T>();
+        if (a.bulk && ctx.tid == 0) bulk_done(ring);     // nobody waits any more: the memory may be reused
         wait_for_cleared_counts();
+        // a wait of the bulk-load sweep that ran out of time: the counts are incomplete; bin 0 says so
+        if (!ok) atomicMax(a.counts, 0xffffffffu);
         for (int b = ctx.tid; b < a.nbins; b += T) {
             unsigned s = 0;
             if (a.lane_private) {

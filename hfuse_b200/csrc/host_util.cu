@@ -73,7 +73,7 @@ int hfuse_tune_set_share(const char* pair, int permille) {
 int hfuse_tune_option(const char* name, int value) {
     if (!name) return HFUSE_ERR_BAD_ARG;
     if (strcmp(name, "im2col_store_path") != 0 && strcmp(name, "exchange_pair_pool") != 0 &&
-        strcmp(name, "bnstats_load_path") != 0) return HFUSE_ERR_UNKNOWN_PAIR;
+        strcmp(name, "bnstats_load_path") != 0 && strcmp(name, "histc_load_path") != 0) return HFUSE_ERR_UNKNOWN_PAIR;
     if (value < -1 || value > 1) return HFUSE_ERR_BAD_ARG;
     std::lock_guard<std::mutex> lk(hfuse::tune_mutex());
     if (value < 0) hfuse::option_table().erase(name);

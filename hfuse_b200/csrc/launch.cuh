@@ -102,6 +102,8 @@ inline Tune tune_get(const char* name) {
 // of them to the statistics range (fused_share_kernel, hfuse_tune_set_share).
 // "bnstats_load_path": -1 (unset) = the compiled choice of each kernel and pair, 0 = 16-byte loads into
 // registers everywhere, 1 = bulk (TMA) copies into shared memory wherever the shape allows it.
+// "histc_load_path": the same choice for the histogram role (up to 256 bins): 0 = 16-byte loads into registers,
+// 1 = bulk (TMA) copies into a ring of shared-memory buffers with "full" and "empty" mbarriers.
 inline std::map<std::string, int>& option_table() {
     static std::map<std::string, int> t;
     return t;

@@ -352,7 +352,8 @@ HFUSE_API int hfuse_sia_ethash_search_sharded(HFUSE_SIA_PARAMS(a_), HFUSE_ETHASH
 HFUSE_API int hfuse_tune_set(const char* pair, int variant, int blocks_per_sm);
 HFUSE_API int hfuse_tune_describe(const char* pair, int variant, char* buf, size_t buflen);
 /* Index of the compiled default variant of a kernel or pair (what runs while hfuse_tune_set has
- * not chosen another one), or HFUSE_ERR_UNKNOWN_PAIR. */
+ * not chosen another one), or HFUSE_ERR_UNKNOWN_PAIR.  "upsample_bnstats_allreduce_wide" names the
+ * exchange pair's default with more than four ranks. */
 HFUSE_API int hfuse_tune_default(const char* pair);
 /* "upsample_bnstats_allreduce" only: per mille (0..1000, -1 = compiled default) of the upsample's
  * items that the statistics thread range takes over between sending its moments to the peers and
@@ -370,6 +371,10 @@ HFUSE_API int hfuse_tune_set_share(const char* pair, int permille);
  *       0 = 16-byte loads into registers; 1 = bulk (TMA) copies of whole rows into two
  *       shared-memory buffers, completion counted on an mbarrier, summed from shared memory;
  *       -1 (the default) = the compiled choice per kernel or pair.  Same statistics to rounding.
+ *   "histc_load_path": how the histogram role reads its input (up to 256 bins).  0 = 16-byte loads
+ *       into registers; 1 = one thread brings chunks of the input into a ring of shared-memory
+ *       buffers with bulk (TMA) copies ("full" and "empty" mbarriers per buffer) and the others count
+ *       out of shared memory; -1 (the default) = the compiled choice.  Same counts either way.
  *   "exchange_pair_pool": how hfuse_upsample_bnstats_allreduce_f32 divides the upsample between its
  *       two thread ranges.  1 = every warp of the block draws 32-item chunks from one cursor (the
  *       statistics range joins after it has sent its moments); 0 = a fixed share goes to the

@@ -99,6 +99,8 @@ def test_fused_search_needs_two_different_hit_records_and_a_count_that_fits_the_
     assert L.hfuse_tune_option(b"exchange_pair_pool", -1) == 0
     assert L.hfuse_tune_option(b"bnstats_load_path", 1) == 0
     assert L.hfuse_tune_option(b"bnstats_load_path", -1) == 0
+    assert L.hfuse_tune_option(b"histc_load_path", 1) == 0
+    assert L.hfuse_tune_option(b"histc_load_path", -1) == 0
 
 
 def test_ops_refuse_cpu_tensors():

@@ -172,19 +172,22 @@ def test_histc_edge_values_ragged_sizes_and_dirty_counts_for_every_variant(dev):
         edges = [lo, hi, np.nextafter(f32(lo), f32(-np.inf)), np.nextafter(f32(lo), f32(np.inf)),
                  np.nextafter(f32(hi), f32(-np.inf)), np.nextafter(f32(hi), f32(np.inf)),
                  float("inf"), -float("inf"), float("nan"), -0.0, 0.0]
-        for n in (11, 4 * 1024 + 1, group - 4, group, group + 7, 2 * group + 4 * 77 + 3):
+        for n in (11, 4 * 1024 + 1, 8 * 768 * 148 + 5, group - 4, group, group + 7, 2 * group + 4 * 77 + 3):
             x = torch.randn(n, generator=g) * 1.5
             x[:len(edges)] = torch.tensor([float(e) for e in edges])
             want = dl.histc_numpy(x.numpy(), nb, lo, hi)
             xd = x.to(dev)
             op = ops.Histc(xd, nb, lo, hi)
-            for v in range(len(_lib.tune_variants("histc"))):
-                _lib.tune_set("histc", v, 0)
-                try:
-                    op.counts.fill_(-7)
-                    assert np.array_equal(_u32(ops.run(op)), want), (nb, lo, hi, n, v)
-                finally:
-                    _lib.tune_set("histc", -1, 0)
+            for path in (0, 1):         # 16-byte loads into registers; bulk copies into a shared-memory ring (up to 256 bins)
+                for v in range(len(_lib.tune_variants("histc"))):
+                    _lib.tune_set("histc", v, 0)
+                    _lib.tune_option("histc_load_path", path)
+                    try:
+                        op.counts.fill_(-7)
+                        assert np.array_equal(_u32(ops.run(op)), want), (nb, lo, hi, n, v, path)
+                    finally:
+                        _lib.tune_set("histc", -1, 0)
+                        _lib.tune_option("histc_load_path", -1)
             # two calls in a row into the same buffer: the second must not see the first's counts
             ops.run(op)
             assert np.array_equal(_u32(ops.run(op)), want)

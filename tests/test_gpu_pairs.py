@@ -22,7 +22,7 @@ def _mk(key, dev, big=False):
     if key == "upsample":
         return ops.Upsample(torch.rand(3, 5, 12, 16, generator=g).to(dev), scale_factor=2)
     if key == "histc":
-        return ops.Histc(torch.randn(200_003, generator=g).to(dev), 64, -3.0, 3.0)
+        return ops.Histc(torch.randn(2_000_003, generator=g).to(dev), 64, -3.0, 3.0)    # several chunks per block on the bulk-load path
     raise KeyError(key)
 
 
@@ -44,9 +44,13 @@ def test_fused_equals_standalone_for_every_variant(dev, pair):
     ops.run(b)
     ra, rb = _snapshot(a), _snapshot(b)
     try:
-        for path in ((0, 1) if "im2col" in pair else (None,)):      # both store paths of the im2col role
-            if path is not None:
-                _lib.tune_option("im2col_store_path", path)
+        paths = [(ip, hp) for ip in ((0, 1) if "im2col" in pair else (None,))       # both store paths of the im2col role
+                 for hp in ((0, 1) if "histc" in pair else (None,))]                # both load paths of the histogram role
+        for path in paths:
+            if path[0] is not None:
+                _lib.tune_option("im2col_store_path", path[0])
+            if path[1] is not None:
+                _lib.tune_option("histc_load_path", path[1])
             for v in range(len(_lib.tune_variants(pair))):
                 _lib.tune_set(pair, v, 0)
                 for t in a.result() if isinstance(a.result(), tuple) else (a.result(),):
@@ -67,6 +71,7 @@ def test_fused_equals_standalone_for_every_variant(dev, pair):
     finally:
         _lib.tune_set(pair, -1, 0)
         _lib.tune_option("im2col_store_path", -1)
+        _lib.tune_option("histc_load_path", -1)
 
 
 def test_pair_config0_against_oracle(dev):

@@ -23,8 +23,8 @@ def test_sweep_results_are_written_into_the_default_tables(tmp_path):
     before = (csrc / "crypto_tuned.inc").read_text()
     sweep = {"solo": {"histc": {"best": 4, "variant": "512:0:4", "us": 1.0},
                       "im2col": {"best": 1, "variant": "256:0:8", "us": 1.0, "im2col_bulk": 0}},
-             "pair": {"im2col_histc": {"best": 3, "variant": "256:256:3", "us": 1.0, "im2col_bulk": 1},
-                      "histc_bnstats": {"best": 9, "variant": "512:256:1", "us": 1.0}}}
+             "pair": {"im2col_histc": {"best": 3, "variant": "256:256:3", "us": 1.0, "im2col_bulk": 1, "histc_bulk": 1},
+                      "histc_bnstats": {"best": 9, "variant": "512:256:1", "us": 1.0, "bnstats_bulk": 1, "histc_bulk": 0}}}
     path = tmp_path / "tune.json"
     path.write_text("some log line\n" + json.dumps(sweep))          # text ahead of the JSON is skipped
     apply_tuning.apply(str(path), str(csrc))
@@ -32,6 +32,8 @@ def test_sweep_results_are_written_into_the_default_tables(tmp_path):
     assert _value(dl, "kDefaultSolo_histc") == 4 and _value(dl, "kDefaultSolo_im2col") == 1
     assert _value(dl, "kDefaultPair_im2col_histc") == 3 and _value(dl, "kDefaultPair_histc_bnstats") == 9
     assert _value(dl, "kIm2colBulk_im2col") == 0 and _value(dl, "kIm2colBulk_im2col_histc") == 1
+    assert _value(dl, "kHistcBulk_im2col_histc") == 1 and _value(dl, "kHistcBulk_histc_bnstats") == 0
+    assert _value(dl, "kBnStatsBulk_histc_bnstats") == 1
     assert (csrc / "crypto_tuned.inc").read_text() == before          # nothing in the sweep for it
     share = {"pair": "upsample_bnstats_allreduce", "n_gpus": 8, "best": {"index": 16, "share_permille": 300}}
     path.write_text(json.dumps(share))
@@ -39,12 +41,20 @@ def test_sweep_results_are_written_into_the_default_tables(tmp_path):
     dl = (csrc / "dl_tuned.inc").read_text()
     assert _value(dl, "kDefaultPair_upsample_bnstats_allreduce_wide") == 16
     assert _value(dl, "kDefaultShare_upsample_bnstats_allreduce_wide") == 300
-    share["best"] = {"index": 16, "share_permille": -1, "pool": True}
+    share["best"] = {"index": 16, "share_permille": -1, "pool": True, "bnstats_bulk": 1}       # cursor form, eight ranks
     path.write_text(json.dumps(share))
     apply_tuning.apply_share(str(path), str(csrc))
     dl = (csrc / "dl_tuned.inc").read_text()
     assert _value(dl, "kDefaultPool_upsample_bnstats_allreduce") == 1
-    assert _value(dl, "kDefaultPoolPair_upsample_bnstats_allreduce") == 16
+    assert _value(dl, "kDefaultPoolPair_upsample_bnstats_allreduce_wide") == 16
+    assert _value(dl, "kBnStatsBulk_upsample_bnstats_allreduce") == 1
+    share["n_gpus"], share["best"] = 4, {"index": 7, "share_permille": -1, "pool": True}          # up to four ranks
+    path.write_text(json.dumps(share))
+    apply_tuning.apply_share(str(path), str(csrc))
+    dl = (csrc / "dl_tuned.inc").read_text()
+    assert _value(dl, "kDefaultPoolPair_upsample_bnstats_allreduce") == 7
+    assert _value(dl, "kDefaultPoolPair_upsample_bnstats_allreduce_wide") == 16
+    assert _value(dl, "kBnStatsBulk_upsample_bnstats_allreduce") == 0
     share["n_gpus"], share["best"] = 2, {"index": 20, "share_permille": 100}
     path.write_text(json.dumps(share))
     apply_tuning.apply_share(str(path), str(csrc))
