@@ -4,7 +4,7 @@
 // four to nine times what they read, and HBM3e turns out to sustain less for such a mix, however
 // the stores are issued.  This kernel moves a given number of bytes in and a given number out
 // with 16-byte loads and 32-byte streaming stores and nothing else, so a caller can time the
-// same mix as the kernel it wants to judge.
+// same mix as the kernel it is to be compared with.
 #include "launch.cuh"
 
 namespace hfuse {
