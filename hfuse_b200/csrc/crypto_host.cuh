@@ -136,8 +136,9 @@ int prep_eth(HFUSE_ETHASH_PARAMS(), EthashArgs& a) {
     X(0, 128, 128, 2) X(1, 128, 128, 3) X(2, 128, 128, 4) X(3, 256, 128, 2) X(4, 128, 256, 2)         \
     X(5, 384, 128, 1) X(6, 128, 384, 1) X(7, 256, 256, 1) X(8, 256, 256, 2) X(9, 128, 128, 1)         \
     X(10, 384, 128, 2) X(11, 128, 384, 2) X(12, 256, 128, 1) X(13, 128, 256, 1)         \
-    X(14, 64, 448, 1) X(15, 448, 64, 1) X(16, 64, 192, 2) X(17, 192, 64, 2) X(18, 32, 224, 4) X(19, 224, 32, 4)
-constexpr int kCryptoPairVariants = 20;
+    X(14, 64, 448, 1) X(15, 448, 64, 1) X(16, 64, 192, 2) X(17, 192, 64, 2) X(18, 32, 224, 4) X(19, 224, 32, 4)         \
+    X(20, 32, 352, 2) X(21, 352, 32, 2) X(22, 64, 320, 2) X(23, 320, 64, 2) X(24, 32, 224, 3) X(25, 224, 32, 3)
+constexpr int kCryptoPairVariants = 26;
 #define CRYPTO_SOLO_VARIANTS(X) \
     X(0, 128, 4) X(1, 128, 6) X(2, 128, 8) X(3, 256, 2) X(4, 256, 3) X(5, 256, 4) X(6, 128, 3) X(7, 128, 5) X(8, 128, 2)
 // the same sweep in work-queue form (warps draw chunks of nonces from the cursor in the hits record)
