@@ -43,6 +43,7 @@ def test_tuning_table():
     assert _lib.lib().hfuse_tune_set(b"no_such_pair", 0, 0) == -7
     assert _lib.lib().hfuse_tune_default(b"no_such_pair") == -7
     assert _lib.tune_default("upsample_bnstats_allreduce") in _lib.tune_variants("upsample_bnstats_allreduce")
+    assert _lib.tune_default("upsample_bnstats_allreduce_wide") in _lib.tune_variants("upsample_bnstats_allreduce")   # beyond four ranks
     assert _lib.lib().hfuse_tune_set(b"im2col_maxpool", 999, 0) < 0
     _lib.tune_set("im2col_maxpool", 1, 2)
     _lib.tune_set("im2col_maxpool", -1, 0)
